@@ -7,7 +7,9 @@ from .lepizen import ARCHITECTURE as LEPIZEN_ARCHITECTURE
 from .lepizen import LepizenConfig
 from .mozepel import ARCHITECTURE as MOZEPEL_ARCHITECTURE
 from .mozepel import MozepelConfig
+from .puputar import ARCHITECTURE as PUPUTAR_ARCHITECTURE
+from .puputar import PuputarConfig
 
-__all__ = ["LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
+__all__ = ["PuputarConfig", "PUPUTAR_ARCHITECTURE", "LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
            "Qwen2Config", "QWEN2_ARCHITECTURE", "LepizenConfig", "LEPIZEN_ARCHITECTURE", "MozepelConfig", "MOZEPEL_ARCHITECTURE",
            "read_config_json"]

@@ -60,6 +60,7 @@ struct AttnParams {
   int* status;
   int leave_states;          // the key runs' states stay unmerged in the scratch memory: the caller merges them
   int q_stride, out_stride;
+  int v_pitch;               // numbers between the starts of two positions' values in v_pages (DV: packed)
   int max_pages, num_pages, page_size, page_shift;
   int num_seqs, total_tokens;
   int early_tiles;           // decode: key tiles of settled positions asked for before the dependency wait (0: none)
@@ -107,7 +108,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // outside [lo, hi) are zero-filled so that masked columns never meet NaNs.
 template <int NWARPS, int WIDTH = HD>
 __device__ __forceinline__ void load_tile(const AttnParams& p, const __nv_bfloat16* pages, const int* table, int kvh,
-                                          __nv_bfloat16* tile, int k0, int lo, int hi, bool& bad_page) {
+                                          __nv_bfloat16* tile, int k0, int lo, int hi, bool& bad_page, int pitch = WIDTH) {
   constexpr int CHUNKS = WIDTH / 8;      // 16-byte chunks per row
   for (int c = threadIdx.x; c < BKV * CHUNKS; c += NWARPS * 32) {
     const int j = c / CHUNKS, part = c - j * CHUNKS;
@@ -119,7 +120,7 @@ __device__ __forceinline__ void load_tile(const AttnParams& p, const __nv_bfloat
       const int page_index = kpos >> p.page_shift;
       const int page = page_index < p.max_pages ? table[page_index] : -1;
       if (page >= 0 && page < p.num_pages) {
-        src = pages + ((((size_t)page * p.kv_heads + kvh) << p.page_shift) + (kpos & (p.page_size - 1))) * WIDTH + part * 8;
+        src = pages + ((((size_t)page * p.kv_heads + kvh) << p.page_shift) + (kpos & (p.page_size - 1))) * (size_t)pitch + part * 8;
         bytes = 16;
       } else {
         bad_page = true;
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int k_first = lo / BKV * BKV;
   const int num_tiles = (hi - k_first + BKV - 1) / BKV;
   load_tile<NWARPS>(p, p.k_pages, table, kvh, sK, k_first, lo, hi, bad_page);
-  load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV, k_first, lo, hi, bad_page);
+  load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV, k_first, lo, hi, bad_page, p.v_pitch);
   cp_async_commit();
 
   for (int it = 0; it < num_tiles; ++it) {
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int k0 = k_first + it * BKV;
     if (it + 1 < num_tiles) {
       load_tile<NWARPS>(p, p.k_pages, table, kvh, sK + (stage ^ 1) * BKV * ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
-      load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV + (stage ^ 1) * BKV * V_ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
+      load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV + (stage ^ 1) * BKV * V_ROW_ELEMS, k0 + BKV, lo, hi, bad_page, p.v_pitch);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < num_tiles) {
       load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, stages + s * STAGE_ELEMS, k_first + s * BKV, lo, hi, bad_page);
-      load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, stages + s * STAGE_ELEMS + BKV * ROW_ELEMS, k_first + s * BKV, lo, hi, bad_page);
+      load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, stages + s * STAGE_ELEMS + BKV * ROW_ELEMS, k_first + s * BKV, lo, hi, bad_page, p.v_pitch);
     }
     cp_async_commit();
   }
@@ -422,7 +423,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
       if (next < num_tiles) {
         __nv_bfloat16* dst = stages + (next % DEC_STAGES) * STAGE_ELEMS;
         load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, dst, k_first + next * BKV, lo, hi, bad_page);
-        load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, dst + BKV * ROW_ELEMS, k_first + next * BKV, lo, hi, bad_page);
+        load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, dst + BKV * ROW_ELEMS, k_first + next * BKV, lo, hi, bad_page, p.v_pitch);
       }
       cp_async_commit();
     }
@@ -1315,7 +1316,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int first_token, const float* sink, int leave_states, cudaStream_t stream) {
+                              int first_token, const float* sink, int leave_states, int v_pitch, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
   TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
@@ -1333,6 +1334,10 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.block_table = block_table; p.q_start = q_start; p.start_pos = start_pos;
   p.out = (__nv_bfloat16*)out; p.status = status; p.sink = sink;
   p.leave_states = leave_states;
+  if (v_pitch == 0) v_pitch = DV;
+  TGE_REQUIRE(v_pitch >= DV && v_pitch % 8 == 0, "attention_mma: a value pitch of %d (values of %d) must be a multiple of 8", v_pitch, DV);
+  TGE_REQUIRE(v_pitch == DV || !(TGE_TMA_KERNELS), "attention_mma: values inside the keys' entries are not served at equal sizes");
+  p.v_pitch = v_pitch;
   p.q_stride = q_stride; p.out_stride = out_stride;
   p.max_pages = max_pages; p.num_pages = num_pages; p.page_size = page_size;
   p.page_shift = 0;
@@ -1538,7 +1543,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
                               int decode_prefix, int prefix_split_tokens, const float* sink, int leave_states,
-                              cudaStream_t stream) {
+                              int v_pitch, cudaStream_t stream) {
   TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
               decode_prefix, num_seqs);
   TGE_REQUIRE(prefix_split_tokens >= 0 && prefix_split_tokens % BKV == 0,
@@ -1546,14 +1551,14 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
     return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
                               positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
-                              window, split_tokens, scratch, status, 0, sink, leave_states, stream);
+                              window, split_tokens, scratch, status, 0, sink, leave_states, v_pitch, stream);
   const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
                                        start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
-                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, leave_states, stream);
+                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, leave_states, v_pitch, stream);
   if (first < 0) return first;
   const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
                                       num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,
                                       num_seqs - decode_prefix, tokens, max_q_len, max_ctx_len, out, out_stride, heads,
-                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, leave_states, stream);
+                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, leave_states, v_pitch, stream);
   return rest < 0 ? rest : first + rest;
 }

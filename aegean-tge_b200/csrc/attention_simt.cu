@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     const int* __restrict__ block_table, int max_pages, int num_pages, int page_size,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, T* __restrict__ out, int out_stride,
-    int heads, int kv_heads, int head_dim, int value_dim, const float* __restrict__ sink, float scale, int window,
+    int heads, int kv_heads, int head_dim, int value_dim, int v_pitch, const float* __restrict__ sink, float scale, int window,
     int pool, const T* __restrict__ kp_pages, const T* __restrict__ vp_pages, const int* __restrict__ pool_table,
     int pool_max_pages, int pool_num_pages, int* status) {
   const int t = blockIdx.x;
@@ -88,12 +88,12 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
       break;
     }
     const size_t base = ((size_t)page * kv_heads + kvh) * page_size * head_dim;
-    const size_t vbase = ((size_t)page * kv_heads + kvh) * page_size * value_dim;
+    const size_t vbase = ((size_t)page * kv_heads + kvh) * page_size * v_pitch;   // v_pitch: numbers between two values' starts
     const int lo = max(first - page_index * page_size, 0);
     const int hi = min(pos - page_index * page_size, page_size - 1);
     for (int slot = lo; slot <= hi; ++slot) {
       const T* krow = k_pages + base + (size_t)slot * head_dim;
-      const T* vrow = v_pages + vbase + (size_t)slot * value_dim;
+      const T* vrow = v_pages + vbase + (size_t)slot * v_pitch;
       float dot = 0.0f;
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -226,8 +226,13 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
                                const int* positions, const int* seq_of_token, void* out, int out_stride, int tokens,
                                int heads, int kv_heads, int head_dim, int value_dim, const float* sink, float scale,
                                int window, int is_bf16, int pool, const void* kp_pages, const void* vp_pages,
-                               const int* pool_table, int pool_max_pages, int pool_num_pages, int* status,
+                               const int* pool_table, int pool_max_pages, int pool_num_pages, int v_pitch, int* status,
                                cudaStream_t stream) {
+  // v_pitch: numbers between the starts of two positions' values in `v_pages` (0: value_dim, values packed).  A cache
+  // whose values are the leading part of its keys passes the keys' pages twice and the keys' size here.
+  if (v_pitch == 0) v_pitch = value_dim;
+  TGE_REQUIRE(v_pitch >= value_dim, "attention: a value pitch of %d is less than the values' size %d", v_pitch, value_dim);
+  TGE_REQUIRE(pool == 0 || v_pitch == value_dim, "attention: pooled blocks go with packed values");
   TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
   TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE, "attention: head_dim %d outside (0, %d]", head_dim,
@@ -245,12 +250,12 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
     attention_simt_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
         max_pages, num_pages, page_size, positions, seq_of_token, (__nv_bfloat16*)out, out_stride, heads, kv_heads,
-        head_dim, value_dim, sink, scale, window, pool, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages,
+        head_dim, value_dim, v_pitch, sink, scale, window, pool, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages,
         pool_table, pool_max_pages, pool_num_pages, status);
   else
     attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
         (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_pages, num_pages,
-        page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, sink, scale,
+        page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, v_pitch, sink, scale,
         window, pool, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, status);
   return tge_launched("attention_simt", 1);
 }

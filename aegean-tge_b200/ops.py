@@ -93,11 +93,31 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
-                                             _c_ptr, _c_ptr])
+                                             _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_attention_pooled_merge", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                                      _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
                                                      _c_ptr])
+        _declare(lib, "tge_group_norm", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                         _c_ptr, _c_ptr])
+        _declare(lib, "tge_token_shift", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                          _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_latent_prepare", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float,
+                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                             _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_head_linear", [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_int, _c_ll, _c_int,
+                                          _c_int, _c_int, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_rotate_interleaved", [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int,
+                                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_router_topk", [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                                          _c_ptr])
+        _declare(lib, "tge_activation", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr])
+        _declare(lib, "tge_experts_direct", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                             _c_int, _c_int, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_experts_group", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_ptr])
+        _declare(lib, "tge_experts_combine_add", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int,
+                                                  _c_int, _c_ptr])
         _declare(lib, "tge_to_run_dtype", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
         _declare(lib, "tge_scale_add_norm", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float,
                                              _c_float, _c_ptr])
@@ -141,7 +161,7 @@ def attention_lib(head_dim: int, value_dim: int = 0) -> ctypes.CDLL:
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
                                             _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
-                                            _c_int, _c_ptr])
+                                            _c_int, _c_int, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim or lib.tge_attention_mma_value_dim() != value_dim:
@@ -710,7 +730,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
               force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0,
               sink: Optional[torch.Tensor] = None, pool: int = 0, pooled_k: Optional[torch.Tensor] = None,
-              pooled_v: Optional[torch.Tensor] = None, pool_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+              pooled_v: Optional[torch.Tensor] = None, pool_table: Optional[torch.Tensor] = None,
+              values_in_keys: int = 0) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
@@ -726,12 +747,19 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     every block of ``pool`` positions that lies wholly before them, in the same softmax; ``pooled_k`` /
     ``pooled_v`` are pages shaped like the keys' and values', entry b of a request where position b would be, found
     through ``pool_table``.  Served by the CUDA-core kernel.
+    ``values_in_keys`` > 0: a position's value is the first that many numbers of its key entry (a latent cache whose
+    entries serve as keys whole and as values in part); ``v_pages`` is then not used and may be None.
     """
+    v_pitch = 0
+    if values_in_keys:
+        if not 0 < values_in_keys <= head_dim or pool:
+            raise KernelError(f"attention: values of {values_in_keys} inside keys of {head_dim} (and no pooled blocks)")
+        v_pages, v_pitch = k_pages[..., :values_in_keys], head_dim
     _want(q, "queries", _FLOAT, contiguous=False)
     q_stride = _rows_2d(q, "queries")
     tokens = q.shape[0]
     _want(k_pages, "k pages", q.dtype)
-    _want(v_pages, "v pages", q.dtype)
+    _want(v_pages, "v pages", q.dtype, contiguous=not values_in_keys)
     for name, t in (("block table", block_table), ("q_start", q_start), ("start_pos", start_pos),
                     ("positions", positions), ("seq_of_token", seq_of_token)):
         _want(t, name, torch.int32)
@@ -766,7 +794,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                               f"and {tuple(pooled_v.shape)}")
         pool_pages, pool_width = pooled_k.shape[0], pool_table.shape[1]
     use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
-               and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim))
+               and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim)
+               and not (v_pitch and value_dim == head_dim))
     if use_mma:
         lib = attention_lib(head_dim, value_dim)
         prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 and not pool else 0
@@ -799,7 +828,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
                                      split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
-                                     _ptr(sink), int(bool(pool)), _stream()), lib)
+                                     _ptr(sink), int(bool(pool)), v_pitch, _stream()), lib)
         if pool:
             core_lib = core()
             states = scratch.data_ptr()
@@ -817,7 +846,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                   seq_of_token.data_ptr(), out.data_ptr(), out_stride, tokens, heads, kv_heads,
                                   head_dim, value_dim, _ptr(sink), float(scale), window, int(q.dtype == torch.bfloat16),
                                   int(pool), _ptr(pooled_k), _ptr(pooled_v), _ptr(pool_table), pool_width, pool_pages,
-                                  status_word().data_ptr(), _stream()), lib)
+                                  v_pitch, status_word().data_ptr(), _stream()), lib)
     return out
 
 
@@ -1133,3 +1162,250 @@ def sample_cuts(scores: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
                                min_p.data_ptr(), uniform.data_ptr(), sort_prob.data_ptr(), sort_index.data_ptr(),
                                out.data_ptr(), rows, vocab, int(skip_uncut), _stream()), lib)
     return out
+
+
+# ----------------------------------------------------------------------------
+# norms in groups, token shift
+# ----------------------------------------------------------------------------
+def group_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out_dtype: torch.dtype,
+               rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS norm in ``groups`` equal consecutive parts of every float32 row (each part over its own root mean
+    square), times ``weight``; rows optionally gathered by ``rows``.  ``out_dtype`` float32 or bfloat16; ``out`` may
+    be ``x`` itself (float32, no gather): the stream normalised in place."""
+    _want(x, "norm input", torch.float32)
+    _want(weight, "norm weight", torch.float32)
+    src_rows, width = x.shape
+    if weight.numel() != width:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {width}")
+    out_rows = src_rows if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, "norm row index", torch.int32)
+    if out is None:
+        out = torch.empty((out_rows, width), dtype=out_dtype, device=x.device)
+    _want(out, "norm output", _FLOAT)
+    if tuple(out.shape) != (out_rows, width) or (out.data_ptr() == x.data_ptr() and (rows is not None or out.dtype != x.dtype)):
+        raise KernelError("group_norm: the output must be [rows, width], and may be the input only ungathered in float32")
+    lib = core()
+    _check(lib.tge_group_norm(x.data_ptr(), weight.data_ptr(), _ptr(rows), out.data_ptr(), int(out.dtype == torch.bfloat16),
+                              out_rows, src_rows, width, int(groups), float(eps), status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,
+                q_start: torch.Tensor, start_pos: torch.Tensor, num_seqs: int, update: bool = True) -> torch.Tensor:
+    """out_t = h_t + (h_(t-1) - h_t) * mu, the row before a portion's first token taken from the request's row of
+    ``state`` (float32 [slots, width]; zeros at position 0); with ``update`` every portion's last row of ``h`` then
+    replaces its request's row of ``state``."""
+    _want(h, "rows", _FLOAT)
+    _want(mu, "shift weight", torch.float32)
+    _want(state, "shift state", torch.float32)
+    for name, t in (("slots", slots), ("seq_of_token", seq_of_token), ("q_start", q_start), ("start_pos", start_pos)):
+        _want(t, name, torch.int32)
+    tokens, width = h.shape
+    if mu.numel() != width or state.dim() != 2 or state.shape[1] != width:
+        raise KernelError(f"token_shift: weight of {mu.numel()} and state {tuple(state.shape)} for rows of {width}")
+    out = torch.empty_like(h)
+    lib = core()
+    _check(lib.tge_token_shift(h.data_ptr(), int(h.dtype == torch.bfloat16), mu.data_ptr(), state.data_ptr(), slots.data_ptr(),
+                               state.shape[0], seq_of_token.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(), out.data_ptr(),
+                               tokens, int(num_seqs), width, int(update), status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+# ----------------------------------------------------------------------------
+# attention over a latent cache
+# ----------------------------------------------------------------------------
+def latent_prepare(raw: torch.Tensor, q_rank: int, kv_rank: int, rot: int, gate_n: int, has_kv: bool,
+                   q_weight: torch.Tensor, kv_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], rot_dims: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], out_dtype: torch.dtype):
+    """From the float32 rows ``raw`` = [query latent | kv latent | shared key part | gate logits] (the middle two only
+    with ``has_kv``): the RMS-normed query latent (run dtype [T, q_rank]) and the logistic gate (float32 [T, gate_n]);
+    with ``pages`` ([num_pages, 1, page_size, kv_rank + rot]) the RMS-normed kv latent and the shared key part, its
+    first ``rot_dims`` numbers rotated in neighbouring pairs by the float32 tables ``cos`` / ``sin`` [positions,
+    rot_dims / 2], are written into each token's entry."""
+    _want(raw, "latent rows", torch.float32, contiguous=False)
+    ld = _rows_2d(raw, "latent rows")
+    tokens = raw.shape[0]
+    _want(q_weight, "query latent norm weight", torch.float32)
+    if q_weight.numel() != q_rank:
+        raise KernelError(f"latent_prepare: a norm weight of {q_weight.numel()} for a query latent of {q_rank}")
+    max_pages = num_pages = page_size = max_positions = 0
+    if has_kv:
+        _want(kv_weight, "kv latent norm weight", torch.float32)
+        if kv_weight.numel() != kv_rank:
+            raise KernelError(f"latent_prepare: a norm weight of {kv_weight.numel()} for a kv latent of {kv_rank}")
+    if has_kv and pages is not None:
+        _want(pages, "latent pages", out_dtype)
+        _want(block_table, "block table", torch.int32)
+        if pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] != kv_rank + rot:
+            raise KernelError(f"latent_prepare: pages must be [pages, 1, page_size, {kv_rank + rot}], got {tuple(pages.shape)}")
+        num_pages, page_size, max_pages = pages.shape[0], pages.shape[2], block_table.shape[1]
+        max_positions = 2 ** 31 - 1
+        if rot_dims:
+            _want(cos, "cos table", torch.float32)
+            _want(sin, "sin table", torch.float32)
+            if cos.shape != sin.shape or cos.shape[1] != rot_dims // 2:
+                raise KernelError(f"latent_prepare: tables {tuple(cos.shape)} for {rot_dims} rotated numbers")
+            max_positions = cos.shape[0]
+    _want(positions, "positions", torch.int32)
+    _want(seq_of_token, "seq_of_token", torch.int32)
+    q_latent = torch.empty((tokens, q_rank), dtype=out_dtype, device=raw.device)
+    gate = torch.empty((tokens, gate_n), dtype=torch.float32, device=raw.device)
+    lib = core()
+    _check(lib.tge_latent_prepare(raw.data_ptr(), ld, q_rank, kv_rank, rot, gate_n, int(has_kv), q_weight.data_ptr(),
+                                  _ptr(kv_weight), float(eps), _ptr(cos), _ptr(sin), rot_dims, max_positions,
+                                  positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table), max_pages, num_pages,
+                                  page_size, _ptr(pages) if has_kv else None, q_latent.data_ptr(), gate.data_ptr(),
+                                  int(out_dtype == torch.bfloat16), tokens, status_word().data_ptr(), _stream()), lib)
+    return q_latent, gate
+
+
+def head_linear(x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int,
+                gate: Optional[torch.Tensor] = None, gate_mode: int = 0) -> torch.Tensor:
+    """A product per head: out[t, n * out_head + j] = g * sum_k x[t, n * x_head + k] * w[n, j, k] for j < w.shape[1],
+    k < w.shape[2].  ``x`` and ``out`` are 2-D with dense rows (views are fine; a head's run may be narrower than its
+    stride).  ``gate`` float32 [T, heads] (``gate_mode`` 1) or [T, heads * outputs] (2) multiplies the result."""
+    _want(x, "head_linear input", _FLOAT, contiguous=False)
+    _want(w, "head_linear weight", x.dtype)
+    _want(out, "head_linear output", x.dtype, contiguous=False)
+    heads, n_out, k_in = w.shape
+    tokens = x.shape[0]
+    ldx, ldo = _rows_2d(x, "head_linear input"), _rows_2d(out, "head_linear output")
+    if (out.shape[0] != tokens or (heads - 1) * x_head + k_in > x.shape[1] or (heads - 1) * out_head + n_out > out.shape[1]
+            or x_head < k_in or out_head < n_out):
+        raise KernelError(f"head_linear: {heads} heads of {k_in} -> {n_out} do not fit rows of {x.shape[1]} and {out.shape[1]}")
+    gate_row = 0
+    if gate_mode:
+        _want(gate, "head_linear gate", torch.float32)
+        gate_row = gate.shape[1]
+        if gate.shape[0] != tokens or gate_row != (heads if gate_mode == 1 else heads * n_out):
+            raise KernelError(f"head_linear: gate {tuple(gate.shape)} for mode {gate_mode}")
+    lib = core()
+    _check(lib.tge_head_linear(x.data_ptr(), ldx, int(x_head), w.data_ptr(), out.data_ptr(), ldo, int(out_head),
+                               _ptr(gate) if gate_mode else None, int(gate_mode), gate_row, tokens, heads, n_out, k_in,
+                               int(x.dtype == torch.bfloat16), _stream()), lib)
+    return out
+
+
+def rotate_interleaved(src: torch.Tensor, src_head: int, dst: torch.Tensor, dst_head: int, heads: int, width: int,
+                       cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor) -> torch.Tensor:
+    """dst[t, n * dst_head + e] = src[t, n * src_head + e] for e < width, with the first ``rot_dims`` numbers of every
+    run rotated in neighbouring pairs: (u, v) at position p -> (u cos a - v sin a, v cos a + u sin a), a = p * f_i,
+    from float32 tables [positions, rot_dims / 2].  Two buffers (or disjoint runs)."""
+    _want(src, "rotation input", _FLOAT, contiguous=False)
+    _want(dst, "rotation output", src.dtype, contiguous=False)
+    _want(positions, "positions", torch.int32)
+    lds, ldd = _rows_2d(src, "rotation input"), _rows_2d(dst, "rotation output")
+    tokens = src.shape[0]
+    if rot_dims:
+        _want(cos, "cos table", torch.float32)
+        _want(sin, "sin table", torch.float32)
+        if cos.shape != sin.shape or cos.shape[1] != rot_dims // 2:
+            raise KernelError(f"rotate_interleaved: tables {tuple(cos.shape)} for {rot_dims} rotated numbers")
+    if (heads - 1) * src_head + width > src.shape[1] or (heads - 1) * dst_head + width > dst.shape[1] or dst.shape[0] != tokens:
+        raise KernelError("rotate_interleaved: the runs do not fit the rows")
+    lib = core()
+    _check(lib.tge_rotate_interleaved(src.data_ptr(), lds, int(src_head), dst.data_ptr(), ldd, int(dst_head), _ptr(cos) if rot_dims else None,
+                                      _ptr(sin) if rot_dims else None, int(rot_dims), cos.shape[0] if rot_dims else 2 ** 31 - 1,
+                                      positions.data_ptr(), tokens, int(heads), int(width), int(src.dtype == torch.bfloat16),
+                                      status_word().data_ptr(), _stream()), lib)
+    return dst
+
+
+# ----------------------------------------------------------------------------
+# routed feed-forward
+# ----------------------------------------------------------------------------
+ACT_RELU_SQUARED, ACT_XIELU = 0, 1
+
+
+def router_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, group_count: int = 1,
+                group_keep: int = 1):
+    """(ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, outputs]: scores = softmax over
+    all outputs; the ``top`` outputs with the largest score + correction are chosen (the lowest index among equals),
+    only inside the ``group_keep`` of ``group_count`` groups of neighbouring outputs whose best such value is largest;
+    weights = the chosen outputs' scores over their sum (+ 1e-20)."""
+    _want(logits, "router logits", torch.float32, contiguous=False)
+    ld = _rows_2d(logits, "router logits")
+    tokens, outputs = logits.shape
+    if correction is not None:
+        _want(correction, "router correction", torch.float32)
+        if correction.numel() != outputs:
+            raise KernelError(f"router_topk: a correction of {correction.numel()} for {outputs} outputs")
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    lib = core()
+    _check(lib.tge_router_topk(logits.data_ptr(), ld, _ptr(correction), tokens, outputs, int(top), int(group_count),
+                               int(group_keep), ids.data_ptr(), weights.data_ptr(), _stream()), lib)
+    return ids, weights
+
+
+def activation(rows: torch.Tensor, kind: int, params: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place on run-dtype rows (a view with dense rows is fine).  ``ACT_RELU_SQUARED``: relu(z)^2.  ``ACT_XIELU``:
+    z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, (p, q) = ``params`` float32 [2]."""
+    _want(rows, "activation rows", _FLOAT, contiguous=False)
+    ld = _rows_2d(rows, "activation rows")
+    if kind == ACT_XIELU:
+        _want(params, "activation parameters", torch.float32)
+        if params.numel() != 2:
+            raise KernelError("activation: two parameters")
+    lib = core()
+    _check(lib.tge_activation(rows.data_ptr(), ld, rows.shape[0], rows.shape[1], int(kind), _ptr(params),
+                              int(rows.dtype == torch.bfloat16), _stream()), lib)
+    return rows
+
+
+def experts_direct(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                   x: torch.Tensor) -> None:
+    """x[t] += sum_k weights[t, k] * (w_down[e] relu(w_up[e] h[t])^2 with e = ids[t, k], or h[t] itself when e is
+    beyond the experts), every pair reading its expert's rows directly: for steps of few tokens.  w_up [experts, ff,
+    width], w_down [experts, width, ff], x float32 [T, width]."""
+    _want(h, "expert input", _FLOAT, contiguous=False)
+    _want(w_up, "expert up weights", h.dtype)
+    _want(w_down, "expert down weights", h.dtype)
+    _want(ids, "expert ids", torch.int32)
+    _want(weights, "expert weights", torch.float32)
+    _want(x, "stream", torch.float32)
+    tokens, width = x.shape
+    experts, ff = w_up.shape[0], w_up.shape[1]
+    top = ids.shape[1]
+    if w_up.shape[2] != width or tuple(w_down.shape) != (experts, width, ff) or h.shape[0] != tokens or h.shape[1] != width:
+        raise KernelError("experts: shapes do not agree")
+    inner = torch.empty((tokens * top, ff), dtype=h.dtype, device=h.device)
+    lib = core()
+    _check(lib.tge_experts_direct(h.data_ptr(), _rows_2d(h, "expert input"), w_up.data_ptr(), w_down.data_ptr(), ids.data_ptr(),
+                                  weights.data_ptr(), inner.data_ptr(), x.data_ptr(), tokens, top, experts, width, ff,
+                                  int(h.dtype == torch.bfloat16), _stream()), lib)
+
+
+def experts_group(h: torch.Tensor, ids: torch.Tensor, experts: int):
+    """Groups the (token, choice) pairs by expert: (place int32 [T * top]: a pair's row among the grouped rows, -1 for
+    choices beyond the experts; offsets int32 [experts + 1]; grouped [T * top, width]: copies of the pairs' input rows,
+    expert e's at offsets[e] .. offsets[e + 1])."""
+    _want(h, "expert input", _FLOAT, contiguous=False)
+    _want(ids, "expert ids", torch.int32)
+    tokens, width = h.shape
+    top = ids.shape[1]
+    place = torch.empty(tokens * top, dtype=torch.int32, device=h.device)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=h.device)
+    grouped = torch.empty((tokens * top, width), dtype=h.dtype, device=h.device)
+    lib = core()
+    _check(lib.tge_experts_group(h.data_ptr(), _rows_2d(h, "expert input"), ids.data_ptr(), place.data_ptr(), offsets.data_ptr(),
+                                 grouped.data_ptr(), tokens, top, int(experts), width, int(h.dtype == torch.bfloat16), _stream()), lib)
+    return place, offsets, grouped
+
+
+def experts_combine_add(outputs: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, h: torch.Tensor,
+                        x: torch.Tensor) -> None:
+    """x[t] += sum_k weights[t, k] * (outputs[place[t, k]] or, where place is -1, h[t]); outputs float32 grouped rows."""
+    _want(outputs, "expert outputs", torch.float32)
+    _want(place, "expert places", torch.int32)
+    _want(weights, "expert weights", torch.float32)
+    _want(h, "expert input", _FLOAT, contiguous=False)
+    _want(x, "stream", torch.float32)
+    tokens, width = x.shape
+    top = weights.shape[1]
+    lib = core()
+    _check(lib.tge_experts_combine_add(outputs.data_ptr(), place.data_ptr(), weights.data_ptr(), h.data_ptr(),
+                                       _rows_2d(h, "expert input"), x.data_ptr(), tokens, top, width,
+                                       int(h.dtype == torch.bfloat16), _stream()), lib)

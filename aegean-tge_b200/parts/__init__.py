@@ -1,5 +1,5 @@
 """Parts a layer is put together from.  Importing this package registers the built-in ones."""
-from . import attention, block, embedding, linear_attention, mlp, norm, rope  # noqa: F401  (registration)
+from . import attention, block, embedding, latent_attention, linear_attention, mlp, norm, rope, routed_mlp  # noqa: F401  (registration)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, BuildEnv, FeedForward,
                    LayerCache, Mixer, Norm, PagedCacheSpec, ParamSpec, Part, PositionEncoding, StateSpec, StepContext,
                    build_part)

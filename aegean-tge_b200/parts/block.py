@@ -33,7 +33,8 @@ class PreNormBlock(Block):
 
 @BLOCKS.register("parallel")
 class ParallelBlock(Block):
-    """h = norm(x); x += m * (mixer(h) + ffn(h)): one norm, both sublayers read its output.
+    """h = norm(x); x += m * (mixer(h) + ffn(h)): one norm, both sublayers read its output.  With a second norm
+    the feed-forward reads its own, x += m * (mixer(norm1(x)) + ffn(norm2(x))), both norms taken of the same x.
 
     params: ``residual_mult`` (m, default 1).  The feed-forward may be absent (x += m * mixer(h)).
 
@@ -49,8 +50,11 @@ class ParallelBlock(Block):
 
     def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, env, params=None):
         super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, env, params)
-        if ffn_norm is not None:
-            raise ValueError("parallel block: it has one norm; the feed-forward reads the mixer's")
+        if ffn_norm is not None and feed_forward is None:
+            if not getattr(ffn_norm, "optional", False):
+                raise ValueError("parallel block: a second norm without a feed-forward to read it")
+            # else: a norm that a checkpoint may hold for a layer without feed-forward: loaded if present, read by
+            # nothing
         self.mult = float(self.params.get("residual_mult", 1.0))
         self.w_out: Optional[torch.Tensor] = None
         self.b_out: Optional[torch.Tensor] = None
@@ -79,7 +83,7 @@ class ParallelBlock(Block):
         # small-batch kernel takes them in (they stay one tensor; both parts keep views of it)
         share = getattr(self.mixer, "share_input_projection", None)
         adopt = getattr(self.feed_forward, "adopt_input_projection", None)
-        if share is not None and adopt is not None:
+        if share is not None and adopt is not None and self.ffn_norm is None:
             view = share(self.feed_forward.input_projection())
             if view is not None:
                 adopt(view)
@@ -92,13 +96,23 @@ class ParallelBlock(Block):
         ops = self.env.ops
         if h is None:
             h = self.mixer_norm.forward(x)
+        # the feed-forward's rows: its own norm of the same x (taken before anything is added), else the mixer's
+        own_rows = self.ffn_norm is not None and self.feed_forward is not None
+        b = self.ffn_norm.forward(x) if own_rows else h
         if self.w_out is None:
             # whole sublayers, added one by one
             if isinstance(h, ops.DeferredRows):
                 h = h.complete()
+                b = b if own_rows else h
+            if self.mult == 1.0:
+                # each sublayer adds its last product (or its weighted sum) into the float32 stream itself
+                self.mixer.forward_add(h, x, ctx, cache)
+                if self.feed_forward is not None:
+                    self.feed_forward.forward_add(b, x, ctx)
+                return None
             ops.add_to_stream(x, self.mixer.forward(h, ctx, cache), alpha=self.mult)
             if self.feed_forward is not None:
-                ops.add_to_stream(x, self.feed_forward.forward(h, ctx), alpha=self.mult)
+                ops.add_to_stream(x, self.feed_forward.forward(b, ctx), alpha=self.mult)
             return None
         tokens = x.shape[0]
         inner = torch.empty((tokens, self.w_out.shape[1]), dtype=self.env.dtype, device=x.device)
@@ -109,7 +123,7 @@ class ParallelBlock(Block):
                 self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
         else:
             if self.feed_forward is not None:
-                self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
+                self.feed_forward.inner(b, ctx, out=inner[:, self.split:])
             self.mixer.inner(h, ctx, cache, out=inner[:, :self.split])
         fused = next_norm.fusable() if next_norm is not None else None
         if fused is not None:

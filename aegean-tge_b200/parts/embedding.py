@@ -11,12 +11,14 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import EMBEDDINGS, HEADS, ParamSpec, Part
+from .base import EMBEDDINGS, HEADS, NORMS, ParamSpec, Part, build_part
 
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    """params: ``vocab_size``, ``hidden_size``.  weights: ``weight``."""
+    """params: ``vocab_size``, ``hidden_size``; optional ``norm`` (a norm's PartSpec: the looked-up rows are
+    normalised before they become the stream; the norm needs ``forward_stream``).  weights: ``weight`` and, with a
+    norm, its parameters as ``norm.<name>``."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -24,18 +26,28 @@ class TokenEmbedding(Part):
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.weight: Optional[torch.Tensor] = None
+        norm = spec.params.get("norm")
+        self.norm = build_part(NORMS, norm, env) if norm is not None else None
+        if self.norm is not None and not hasattr(self.norm, "forward_stream"):
+            raise ValueError(f"token_embedding: norm '{norm.kind}' cannot normalise the stream in place")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.vocab, self.hidden))}
+        specs = {"weight": ParamSpec((self.vocab, self.hidden))}
+        if self.norm is not None:
+            specs.update({f"norm.{name}": param for name, param in self.norm.param_specs().items()})
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
+        if self.norm is not None:
+            self.norm.load({name[len("norm."):]: t for name, t in tensors.items() if name.startswith("norm.")})
 
     def param_bytes(self) -> int:
         return 0        # a step reads the rows of its tokens, not the table
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return self.ops.embedding(self.weight, token_ids)
+        x = self.ops.embedding(self.weight, token_ids)
+        return x if self.norm is None else self.norm.forward_stream(x)
 
 
 @HEADS.register("linear_head")

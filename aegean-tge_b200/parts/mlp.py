@@ -65,11 +65,13 @@ class SwiGLU(FeedForward):
 
 @FEED_FORWARDS.register("dense_mlp")
 class DenseMLP(FeedForward):
-    """The ungated feed-forward: d = Wdown act(Wup h), no biases.
+    """The ungated feed-forward: d = Wdown act(Wup h + bup) + bdown.
 
     params: ``hidden_size``, ``intermediate_size``, ``activation`` (``"gelu"``: 0.5 z (1 + erf(z / sqrt 2)), the
-    default, or ``"gelu_tanh"``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  weights: ``up|down.weight``.
-    The activation is the epilogue of the up product.
+    default; ``"gelu_tanh"``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); ``"xielu"``: with two learned numbers
+    (p, q), z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2), ``bias`` (bool, default
+    False: both products have one).  weights: ``up|down.weight``, with ``bias`` ``up|down.bias``, with xielu ``act``
+    (float32 [2]).  The GELUs are the epilogue of the up product; xielu is a kernel behind it.
     """
     graph_safe = True
     can_defer_norm = True
@@ -80,27 +82,42 @@ class DenseMLP(FeedForward):
         self.hidden = int(spec.params["hidden_size"])
         self.inner_size = int(spec.params["intermediate_size"])
         activation = str(spec.params.get("activation", "gelu"))
-        if activation not in ("gelu", "gelu_tanh"):
+        if activation not in ("gelu", "gelu_tanh", "xielu"):
             raise ValueError(f"dense_mlp: unknown activation '{activation}'")
         if self.hidden <= 0 or self.inner_size <= 0:
             raise ValueError("dense_mlp: sizes must be positive")
         self.activation = activation
+        self.bias = bool(spec.params.get("bias", False))
         self.w_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
+        self.b_up: Optional[torch.Tensor] = None
+        self.b_down: Optional[torch.Tensor] = None
+        self.act: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"up.weight": ParamSpec((self.inner_size, self.hidden)),
-                "down.weight": ParamSpec((self.hidden, self.inner_size))}
+        specs = {"up.weight": ParamSpec((self.inner_size, self.hidden)),
+                 "down.weight": ParamSpec((self.hidden, self.inner_size))}
+        if self.bias:
+            specs["up.bias"] = ParamSpec((self.inner_size,), role="vector")
+            specs["down.bias"] = ParamSpec((self.hidden,), role="vector")
+        if self.activation == "xielu":
+            specs["act"] = ParamSpec((2,), role="vector")
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.w_up = tensors["up.weight"].contiguous()
         self.w_down = tensors["down.weight"].contiguous()
+        if self.bias:
+            self.b_up = tensors["up.bias"].contiguous()
+            self.b_down = tensors["down.bias"].contiguous()
+        if self.activation == "xielu":
+            self.act = tensors["act"].contiguous()
 
     def flops(self, tokens: int, pairs: float) -> float:
         return 2.0 * tokens * 2 * self.inner_size * self.hidden
 
     def epilogue(self) -> int:
-        return self.ops.GEMM_GELU if self.activation == "gelu" else self.ops.GEMM_GELU_TANH
+        return {"gelu": self.ops.GEMM_GELU, "gelu_tanh": self.ops.GEMM_GELU_TANH, "xielu": self.ops.GEMM_STORE}[self.activation]
 
     def input_projection(self) -> torch.Tensor:
         return self.w_up
@@ -110,18 +127,21 @@ class DenseMLP(FeedForward):
         self.w_up = view
 
     def inner(self, h, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return self.ops.linear(h, self.w_up, None, self.epilogue(), out=out)
+        rows = self.ops.linear(h, self.w_up, self.b_up, self.epilogue(), out=out)
+        if self.activation == "xielu":
+            self.ops.activation(rows, self.ops.ACT_XIELU, self.act)
+        return rows
 
     def output_projection(self):
-        return self.w_down, None
+        return self.w_down, self.b_down
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return self.ops.linear(self.inner(h, ctx), self.w_down, None, self.ops.GEMM_STORE)
+        return self.ops.linear(self.inner(h, ctx), self.w_down, self.b_down, self.ops.GEMM_STORE)
 
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None, defer: bool = False):
         a = self.inner(h, ctx)
         fused = next_norm.fusable() if next_norm is not None else None
         if fused is not None:
-            return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype, defer=defer)
-        self.ops.linear(a, self.w_down, None, self.ops.GEMM_ADD_F32, out=x)
+            return self.ops.linear_add_norm(a, self.w_down, self.b_down, x, fused[0], fused[1], self.env.dtype, defer=defer)
+        self.ops.linear(a, self.w_down, self.b_down, self.ops.GEMM_ADD_F32, out=x)
         return None

@@ -100,6 +100,59 @@ class RotaryNeoX(PositionEncoding):
         return self.cos, self.sin, self.rotary
 
 
+def pair_tables(theta: float, dims: int, positions: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of position * theta^(-2i / dims), i < dims / 2, float32 [positions, dims / 2]; frequencies and
+    angles in float64, rounded once."""
+    index = torch.arange(dims // 2, dtype=torch.float64)
+    freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * index / float(dims))
+    angle = torch.arange(positions, dtype=torch.float64)[:, None] * freq[None, :]
+    return torch.cos(angle).float(), torch.sin(angle).float()
+
+
+@POSITIONS.register("rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotation of neighbouring pairs: element 2i is paired with element 2i+1 (i < dims / 2), and the pair (u, v) at
+    position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * theta^(-2i / dims); elements from ``dims`` on
+    pass unchanged.  The fused rotate-and-store kernel pairs halves, not neighbours, so this encoding is applied by a
+    kernel of its own (``apply``), or by a mixer's own kernel from the tables (``pair_tables``).
+
+    params: ``head_dim`` (width of the rotated run), ``theta``, optional ``rotary_dim`` (default head_dim)."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.head_dim = int(spec.params["head_dim"])
+        self.theta = float(spec.params["theta"])
+        self.rotary = int(spec.params.get("rotary_dim", self.head_dim))
+        if self.rotary < 0 or self.rotary % 2 or self.rotary > self.head_dim:
+            raise ValueError(f"rope: rotary width {self.rotary} must be even and within {self.head_dim}")
+        if not self.theta > 0:
+            raise ValueError("rope: theta must be positive")
+        key = ("pairs", self.theta, self.rotary, env.max_positions, str(env.device))
+        if key not in _TABLES:
+            if len(_TABLES) >= 8:
+                _TABLES.pop(next(iter(_TABLES)))
+            cos, sin = pair_tables(self.theta, max(self.rotary, 2), env.max_positions)
+            _TABLES[key] = (cos.to(env.device).contiguous(), sin.to(env.device).contiguous())
+        self.cos, self.sin = _TABLES[key]
+
+    def pair_tables(self) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        return self.cos, self.sin, self.rotary
+
+    def rotary_tables(self):
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        for t in (q, k):
+            tokens, heads, dim = t.shape
+            flat = t.reshape(tokens, heads * dim) if t.is_contiguous() else None
+            if flat is None:
+                # a view into a wider row (q or k inside a q/k/v row): rows stay dense, heads follow one another
+                flat = t.as_strided((tokens, heads * dim), (t.stride(0), 1))
+            before = flat.clone()
+            self.ops.rotate_interleaved(before, dim, flat, dim, heads, dim, self.cos, self.sin, self.rotary, positions)
+
+
 @POSITIONS.register("none")
 class NoPosition(PositionEncoding):
     """Leaves queries and keys as they are."""
