@@ -146,11 +146,37 @@ def route(h, router, correction, top, group_count, group_keep):
     return ids, weights
 
 
-def moe_ff(h, w, prefix, mlp):
+def route_margin(h, router, correction, top, group_count, group_keep):
+    """[T]: how far each row's choice is from another one: the smallest of (the last chosen value minus the best value
+    left inside the kept groups) and (the last kept group's value minus the best group left out)."""
+    z = h @ router.T
+    z = z - z.max(axis=-1, keepdims=True)
+    s = np.exp(z)
+    choice = s / s.sum(axis=-1, keepdims=True) + correction
+    tokens, outputs = choice.shape
+    per = outputs // group_count
+    ids, _ = route(h, router, correction, top, group_count, group_keep)
+    out = np.full(tokens, np.inf)
+    for t in range(tokens):
+        best = np.sort(choice[t].reshape(group_count, per).max(axis=-1))[::-1]
+        if group_keep < group_count:
+            out[t] = best[group_keep - 1] - best[group_keep]
+        kept = np.argsort(-choice[t].reshape(group_count, per).max(axis=-1), kind="stable")[:group_keep]
+        left = [choice[t, i] for g in kept for i in range(g * per, (g + 1) * per) if i not in ids[t]]
+        if left:
+            out[t] = min(out[t], choice[t, ids[t]].min() - max(left))
+    return out
+
+
+def moe_ff(h, w, prefix, mlp, margins=None):
+    """``margins``: a list that receives this layer's :func:`route_margin` (for tests that must know which rows a
+    rounding could route elsewhere)."""
     r = mlp["router"]
     experts, identity = r["experts"], r.get("identity", 0)
     groups = r.get("groups") or {"count": 1, "keep": 1}
     ids, weights = route(h, w[prefix + "router"], w[prefix + "correction"], r["top"], groups["count"], groups["keep"])
+    if margins is not None:
+        margins.append(route_margin(h, w[prefix + "router"], w[prefix + "correction"], r["top"], groups["count"], groups["keep"]))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, weight in zip(ids[t], weights[t]):
@@ -163,8 +189,10 @@ def moe_ff(h, w, prefix, mlp):
 
 
 # ----------------------------------------------------------------------------------------------- the model
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of a whole sequence (and, on request, the stream after every layer [L, T, width])."""
+def forward(config, w, tokens, return_layers=False, margins=None, shift=True):
+    """Logits [T, vocab] of a whole sequence (and, on request, the stream after every layer [L, T, width]).
+    ``margins``: a list that receives every routed layer's :func:`route_margin`; ``shift`` False leaves the token
+    shift out (for tests of the tests)."""
     eps, groups = config["norm"]["eps"], config["norm"].get("groups", 1)
     positions = np.arange(len(tokens))
     x = group_norm(w["embed"][np.asarray(tokens)], w["embed.norm"], groups, eps)
@@ -173,8 +201,11 @@ def forward(config, w, tokens, return_layers=False):
     for n, layer in enumerate(config["layers"]):
         p = f"l{n}."
         m = layer["mixer"]
-        a = token_shift(group_norm(x, w[p + "norm1"], groups, eps), w[p + "shift"])
-        b = group_norm(x, w[p + "norm2"], groups, eps)
+        a = group_norm(x, w[p + "norm1"], groups, eps)
+        if shift:
+            a = token_shift(a, w[p + "shift"])
+        mlp = layer.get("mlp")
+        b = group_norm(x, w[p + "norm2"], groups, eps) if mlp is not None else None
         if m.get("kv_from") is None:
             kept[n] = latent_kv(a, w, p + "mix.", m, eps, positions)
             kv = kept[n]
@@ -182,13 +213,12 @@ def forward(config, w, tokens, return_layers=False):
             kv = kept[m["kv_from"]]
         gate = {"latent_attention": "head", "latent_attention_2": "element"}[layer["type"]]
         mixed = latent_attention(a, w, p + "mix.", m, eps, positions, gate, kv)
-        mlp = layer.get("mlp")
         if mlp is None:
             fed = 0.0
         elif mlp["kind"] == "dense":
             fed = dense_ff(b, w, p + "mlp.")
         else:
-            fed = moe_ff(b, w, p + "mlp.", mlp)
+            fed = moe_ff(b, w, p + "mlp.", mlp, margins)
         x = x + (mixed + fed)
         streams.append(x.copy())
     logits = group_norm(x, w["final.norm"], groups, eps) @ w["head"].T
