@@ -222,7 +222,32 @@ def paired_configs(width: int, heads: int, kv_heads: int, head_dim: int, gated_i
              "mlp": {"kind": "dense", "ff": gated_inner * 3 // 2}}
     lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
                "logit_scale": 1.0, "logit_softcap": 50.0, "layers": [layer] * layers}
-    return {"qwen2": qwen2, "lepizen": lepizen, "mozepel": mozepel_config(width, heads, kv_heads, head_dim, gated_inner, layers, vocab)}
+    return {"qwen2": qwen2, "lepizen": lepizen, "mozepel": mozepel_config(width, heads, kv_heads, head_dim, gated_inner, layers, vocab),
+            "puputar": puputar_config(width, heads, head_dim, gated_inner, layers, vocab)}
+
+
+def puputar_config(width: int, heads: int, head_dim: int, gated_inner: int, layers: int, vocab: int, experts: int = 16,
+                   top: int = 4) -> dict:
+    """A Puputar config.json with the width, heads, head size and layer count of a Qwen2 shape: queries and keys of
+    ``head_dim`` numbers (half of them rotated), values of ``head_dim``, a query latent of a quarter of the width, cache
+    entries of 192 + head_dim / 2 numbers; layers by turns with the dense feed-forward (two matrices of one and a
+    half times the gated inner width) and with ``experts`` small experts and two identity experts of which ``top`` are
+    used (together as wide as the dense one); every fourth layer reads the entries of the routed layer before it."""
+    rot = head_dim // 2
+    mixer = {"heads": heads, "dim": head_dim - rot, "rot_dim": rot, "vdim": head_dim, "q_rank": max(width // 4 // 64 * 64, 64),
+             "kv_rank": 192, "scale": head_dim ** -0.5, "rot": {"base": 500000.0, "dims": rot}}
+    dense = {"kind": "dense", "ff": gated_inner * 3 // 2}
+    routed = {"kind": "moe", "expert": {"ff": max(gated_inner * 3 // 2 // top // 64 * 64, 64)},
+              "router": {"experts": experts, "top": top, "identity": 2, "groups": {"count": 2, "keep": 1}}}
+    out = []
+    for n in range(layers):
+        if n % 2 == 0:
+            out.append({"type": "latent_attention", "mixer": dict(mixer), "mlp": dense})
+        elif n % 4 == 1:
+            out.append({"type": "latent_attention_2", "mixer": dict(mixer), "mlp": routed})
+        else:
+            out.append({"type": "latent_attention_2", "mixer": dict(mixer, kv_from=n - 2), "mlp": routed})
+    return {"architecture": "Puputar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 2}, "layers": out}
 
 
 def mozepel_config(width: int, heads: int, kv_heads: int, head_dim: int, gated_inner: int, layers: int, vocab: int,

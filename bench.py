@@ -15,7 +15,7 @@ portion), the same figures with the engine's default pages of 64 tokens, long
 contexts, and the 14B and 32B shapes.  This engine runs on one GPU: for --gpus
 above 1 it says so and exits with 2.
 
-    python bench.py --compare lepizen|mozepel [--compare-sizes 7b,14b,1.5b] [--steps K]
+    python bench.py --compare lepizen|mozepel|puputar [--compare-sizes 7b,14b,1.5b] [--steps K]
 
 is another measurement and leaves the one above alone: the Lepizen or the Mozepel design beside the Qwen2 design at equal
 width, heads, layers and vocabulary (Lepizen: and parameter count), at sizes of real models' layers (random weights), prefill
@@ -152,7 +152,7 @@ COMPARE_SIZES = {"1.5b": (1536, 12, 2, 128, 8960), "7b": (3584, 28, 4, 128, 1894
 
 
 def compare(args) -> int:
-    """`--compare lepizen` or `--compare mozepel`: Qwen2 and that design at each size, one JSON line."""
+    """`--compare lepizen`, `mozepel` or `puputar`: Qwen2 and that design at each size, one JSON line."""
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -186,7 +186,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=CONFIG_7B["num_hidden_layers"],
                         help="fewer layers than the model has, if memory or time needs it (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="the headline only: no points")
-    parser.add_argument("--compare", choices=["lepizen", "mozepel"], help="instead of the headline: this design beside Qwen2 at equal size")
+    parser.add_argument("--compare", choices=["lepizen", "mozepel", "puputar"], help="instead of the headline: this design beside Qwen2 at equal size")
     parser.add_argument("--compare-sizes", default="7b,14b,1.5b", help="which of 1.5b, 7b, 14b (layer shapes), with commas")
     parser.add_argument("--compare-layers", type=int, default=8, help="layers of each model in --compare")
     args = parser.parse_args()
