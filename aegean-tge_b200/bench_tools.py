@@ -92,7 +92,7 @@ def fill_cache(engine, batch: int, prompt_len: int, chunk: int = 2048, prefix: s
 def decode_step_bytes(engine, names: List[str]) -> float:
     """Bytes a decode step must move: every weight it uses once, and of each live request the cache entries it may
     read (a window's, where there is one) and the fixed-size state it reads and writes."""
-    return engine.model.step_param_bytes() + sum(engine.model.decode_cache_bytes(engine.cache.computed(n)) for n in names)
+    return engine.model.step_param_bytes(len(names)) + sum(engine.model.decode_cache_bytes(engine.cache.computed(n)) for n in names)
 
 
 def bench_decode(engine, batch: int, prompt_len: int, steps: int = 64, warmup: int = 3) -> Dict[str, float]:

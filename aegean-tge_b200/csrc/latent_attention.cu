@@ -13,7 +13,16 @@
 //  * head_linear        - a product per head, out[t, n, :] = W_n x[t, n, :] (queries into the latent space, attended
 //                         latents to values), optionally times a gate per head or per element.
 //  * rotate_interleaved - rotation of neighbouring pairs (2i, 2i+1) by position * frequency_i, from cos/sin tables,
-//                         over the first `rot_dims` numbers of a run; the rest is copied.
+//                         over `rot_dims` numbers of a run from a given place on; the rest is copied.
+//
+// Long prompt portions go another way: many queries meet every key, so it pays to give every head its own keys and
+// values again, [Wuk_n c | kr] and Wuv_n c, in pages of the step's own, and to run ordinary attention with as many
+// key/value heads as heads (smaller rows per head, the fastest kernels).  For that:
+//
+//  * latent_gather      - the latents of every position the step's requests hold, from their cache entries into dense
+//                         rows (the product's input), and the shared key part into every head's key rows.
+//  * latent_scatter     - the product's output, [heads x dim | heads x vdim] per position, into the key and value pages.
+//  * gate_rows          - the logistic gate on the attended rows, per head or per element.
 //
 // Norm statistics, angles (tables), the gate and every accumulation are float32.
 #include "common.cuh"
@@ -137,7 +146,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) rotate_interleaved_kernel(
     const T* __restrict__ src, long long src_row, long long src_head, T* __restrict__ dst, long long dst_row,
     long long dst_head, const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rot_dims,
-    int max_positions, const int* __restrict__ positions, int tokens, int heads, int width, int* status) {
+    int max_positions, const int* __restrict__ positions, int tokens, int heads, int width, int first, int* status) {
   pdl_trigger();
   pdl_wait();
   const long long total = (long long)tokens * heads * width;
@@ -152,12 +161,76 @@ __global__ void __launch_bounds__(256) rotate_interleaved_kernel(
     }
     const T* run = src + (size_t)t * src_row + (size_t)head * src_head;
     float v = to_float<T>(run[e]);
-    if (e < rot_dims) {
-      const int pair = e >> 1;
+    if (e >= first && e < first + rot_dims) {
+      const int pair = (e - first) >> 1;
       const float c = cos_table[(size_t)pos * (rot_dims / 2) + pair], s = sin_table[(size_t)pos * (rot_dims / 2) + pair];
-      v = (e & 1) ? fmaf(v, c, to_float<T>(run[e - 1]) * s) : fmaf(v, c, -to_float<T>(run[e + 1]) * s);
+      v = ((e - first) & 1) ? fmaf(v, c, to_float<T>(run[e - 1]) * s) : fmaf(v, c, -to_float<T>(run[e + 1]) * s);
     }
     dst[(size_t)t * dst_row + (size_t)head * dst_head + e] = from_float<T>(v);
+  }
+}
+
+// One block per position slot of the step's own pages: slot r = page * page_size + offset; page p belongs to request
+// page_seq[p] and is its page_idx[p]-th.  Positions beyond what the request holds give zeros.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_gather_kernel(
+    const T* __restrict__ pages, const int* __restrict__ table, int max_pages, int num_pages, const int* __restrict__ page_seq,
+    const int* __restrict__ page_idx, const int* __restrict__ ctx_len, int page_size, int kv_rank, int rot, int heads, int per,
+    T* __restrict__ latents, T* __restrict__ keys, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int slot = blockIdx.x, p = slot / page_size, off = slot % page_size;
+  const int seq = page_seq[p], index = page_idx[p];
+  const bool held = index * page_size + off < ctx_len[seq];
+  const T* entry = nullptr;
+  if (held) {
+    const int real = index < max_pages ? table[(size_t)seq * max_pages + index] : -1;
+    if (real < 0 || real >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    } else {
+      entry = pages + ((size_t)real * page_size + off) * (kv_rank + rot);
+    }
+  }
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x)
+    latents[(size_t)slot * kv_rank + i] = entry ? entry[i] : from_float<T>(0.0f);
+  const int dim = per - rot;
+  for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
+    const int n = i / rot, d = i % rot;
+    keys[(((size_t)p * heads + n) * page_size + off) * per + dim + d] = entry ? entry[kv_rank + d] : from_float<T>(0.0f);
+  }
+}
+
+// expanded: [slots, ld] = per position [heads x dim plain key parts | heads x vdim values]; keys [pages, heads,
+// page_size, dim + rot], values [pages, heads, page_size, vdim].
+template <typename T>
+__global__ void __launch_bounds__(256) latent_scatter_kernel(const T* __restrict__ expanded, long long ld, int page_size,
+                                                             int heads, int dim, int per, int vdim, T* __restrict__ keys,
+                                                             T* __restrict__ values) {
+  pdl_trigger();
+  pdl_wait();
+  const int slot = blockIdx.x, p = slot / page_size, off = slot % page_size;
+  const T* row = expanded + (size_t)slot * ld;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    const int n = i / dim, d = i % dim;
+    keys[(((size_t)p * heads + n) * page_size + off) * per + d] = row[i];
+  }
+  const T* vrow = row + (size_t)heads * dim;
+  for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
+    const int n = i / vdim, d = i % vdim;
+    values[(((size_t)p * heads + n) * page_size + off) * vdim + d] = vrow[i];
+  }
+}
+
+// x[t, n, j] *= gate[t, n] (mode 1) or gate[t, n * vdim + j] (mode 2), in place.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_rows_kernel(T* __restrict__ x, long long x_row, const float* __restrict__ gate,
+                                                        long long gate_row, int mode, int heads, int vdim) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
+    const float g = gate[(size_t)t * gate_row + (mode == 1 ? i / vdim : i)];
+    x[(size_t)t * x_row + i] = from_float<T>(to_float<T>(x[(size_t)t * x_row + i]) * g);
   }
 }
 
@@ -211,14 +284,15 @@ TGE_API int tge_head_linear(const void* x, long long x_row, long long x_head, co
   return tge_launched("head_linear", 1);
 }
 
-// src / dst: runs of `width` numbers per (token, head), at t * row + n * head (elements); may be the same buffer
-// only when they are the same runs.
+// src / dst: runs of `width` numbers per (token, head), at t * row + n * head (elements), two buffers.  The rotated
+// numbers are those from `first` on; the others are copied.
 TGE_API int tge_rotate_interleaved(const void* src, long long src_row, long long src_head, void* dst, long long dst_row,
                                    long long dst_head, const float* cos_table, const float* sin_table, int rot_dims,
-                                   int max_positions, const int* positions, int tokens, int heads, int width, int is_bf16,
-                                   int* status, cudaStream_t stream) {
+                                   int max_positions, const int* positions, int tokens, int heads, int width, int first,
+                                   int is_bf16, int* status, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && heads > 0 && width > 0, "rotate_interleaved: bad shape");
-  TGE_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= width, "rotate_interleaved: %d rotated numbers of %d", rot_dims, width);
+  TGE_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && first >= 0 && first + rot_dims <= width,
+              "rotate_interleaved: %d rotated numbers from %d on of %d", rot_dims, first, width);
   TGE_REQUIRE(src != dst, "rotate_interleaved: a pair's second number is read after its first is written; give two buffers");
   if (tokens == 0) return 0;
   const long long total = (long long)tokens * heads * width;
@@ -226,10 +300,57 @@ TGE_API int tge_rotate_interleaved(const void* src, long long src_row, long long
   if (is_bf16)
     tge_launch(rotate_interleaved_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)src,
                src_row, src_head, (__nv_bfloat16*)dst, dst_row, dst_head, cos_table, sin_table, rot_dims, max_positions,
-               positions, tokens, heads, width, status);
+               positions, tokens, heads, width, first, status);
   else
     tge_launch(rotate_interleaved_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)src, src_row, src_head,
                (float*)dst, dst_row, dst_head, cos_table, sin_table, rot_dims, max_positions, positions, tokens, heads, width,
-               status);
+               first, status);
   return tge_launched("rotate_interleaved", 1);
+}
+
+// pages: the cache [num_pages, page_size, kv_rank + rot] found through table [seqs, max_pages]; the step's own pages:
+// own_pages of page_size slots, page p being request page_seq[p]'s page_idx[p]-th; ctx_len [seqs]: positions held.
+// latents: [own_pages * page_size, kv_rank]; keys: [own_pages, heads, page_size, per] (only the last `rot` numbers of
+// a row are written here).
+TGE_API int tge_latent_gather(const void* pages, const int* table, int max_pages, int num_pages, const int* page_seq,
+                              const int* page_idx, const int* ctx_len, int own_pages, int page_size, int kv_rank, int rot,
+                              int heads, int per, void* latents, void* keys, int is_bf16, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(own_pages >= 0 && page_size > 0 && kv_rank > 0 && rot >= 0 && heads > 0 && per >= rot && max_pages > 0 && num_pages > 0,
+              "latent_gather: bad shape");
+  if (own_pages == 0) return 0;
+  if (is_bf16)
+    tge_launch(latent_gather_kernel<__nv_bfloat16>, dim3(own_pages * page_size), dim3(128), 0, stream, (const __nv_bfloat16*)pages,
+               table, max_pages, num_pages, page_seq, page_idx, ctx_len, page_size, kv_rank, rot, heads, per,
+               (__nv_bfloat16*)latents, (__nv_bfloat16*)keys, status);
+  else
+    tge_launch(latent_gather_kernel<float>, dim3(own_pages * page_size), dim3(128), 0, stream, (const float*)pages, table,
+               max_pages, num_pages, page_seq, page_idx, ctx_len, page_size, kv_rank, rot, heads, per, (float*)latents,
+               (float*)keys, status);
+  return tge_launched("latent_gather", 1);
+}
+
+TGE_API int tge_latent_scatter(const void* expanded, long long ld, int own_pages, int page_size, int heads, int dim, int per,
+                               int vdim, void* keys, void* values, int is_bf16, cudaStream_t stream) {
+  TGE_REQUIRE(own_pages >= 0 && page_size > 0 && heads > 0 && dim >= 0 && per >= dim && vdim > 0 &&
+              ld >= (long long)heads * (dim + vdim), "latent_scatter: bad shape");
+  if (own_pages == 0) return 0;
+  if (is_bf16)
+    tge_launch(latent_scatter_kernel<__nv_bfloat16>, dim3(own_pages * page_size), dim3(256), 0, stream,
+               (const __nv_bfloat16*)expanded, ld, page_size, heads, dim, per, vdim, (__nv_bfloat16*)keys, (__nv_bfloat16*)values);
+  else
+    tge_launch(latent_scatter_kernel<float>, dim3(own_pages * page_size), dim3(256), 0, stream, (const float*)expanded, ld,
+               page_size, heads, dim, per, vdim, (float*)keys, (float*)values);
+  return tge_launched("latent_scatter", 1);
+}
+
+TGE_API int tge_gate_rows(void* x, long long x_row, const float* gate, long long gate_row, int mode, int tokens, int heads,
+                          int vdim, int is_bf16, cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0 && (mode == 1 || mode == 2) && gate != nullptr, "gate_rows: bad shape");
+  if (tokens == 0) return 0;
+  if (is_bf16)
+    tge_launch(gate_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)x, x_row, gate, gate_row,
+               mode, heads, vdim);
+  else
+    tge_launch(gate_rows_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)x, x_row, gate, gate_row, mode, heads, vdim);
+  return tge_launched("gate_rows", 1);
 }

@@ -7,6 +7,9 @@
 //  * expert_up / expert_down_add - few tokens (a decode step): every (token, chosen expert) pair reads its expert's
 //                       rows directly, one warp per output, and the weighted outputs are added into the float32 stream
 //                       in the order of the choice; outputs beyond the experts are identity experts (the input itself).
+//  * expert_dense_weigh - a step of some tokens that between them choose most experts anyway: every token goes through
+//                       every expert's up matrix in ONE product, this kernel weighs the chosen experts' activated rows
+//                       and zeroes the others, and ONE product with all down matrices side by side adds the sum.
 //  * expert_sort / expert_gather / expert_combine_add - many tokens: the pairs are grouped by expert so that each
 //                       expert's rows form one block of a buffer, which ordinary products then multiply; the last
 //                       kernel adds the weighted rows back into the stream, again in the order of the choice.
@@ -193,7 +196,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) expert_down_add_kernel(const T* __restrict__ inner, const T* __restrict__ w_down,
                                                               const T* __restrict__ h, long long ld_h,
                                                               const int* __restrict__ ids, const float* __restrict__ weights,
-                                                              float* __restrict__ x, int top, int experts, int width, int ff) {
+                                                              float* __restrict__ x, int top, int experts, int width, int ff,
+                                                              long long down_expert, long long down_row) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -205,7 +209,7 @@ __global__ void __launch_bounds__(256) expert_down_add_kernel(const T* __restric
       const int expert = ids[pair];
       const float weight = weights[pair];
       if (expert >= 0 && expert < experts)
-        acc = fmaf(weight, warp_dot<T>(inner + (size_t)pair * ff, w_down + ((size_t)expert * width + n) * ff, ff, lane), acc);
+        acc = fmaf(weight, warp_dot<T>(inner + (size_t)pair * ff, w_down + (size_t)expert * down_expert + (size_t)n * down_row, ff, lane), acc);
       else
         acc = fmaf(weight, to_float<T>(h[(size_t)t * ld_h + n]), acc);
     }
@@ -276,6 +280,44 @@ __global__ void __launch_bounds__(256) expert_combine_add_kernel(const float* __
   }
 }
 
+// The dense path, between its two products.  z [tokens, experts * ff]: every expert's up projection of every token.
+// In place: a token's rows of a chosen expert become weight * relu(z)^2, all others zero, so that ONE product with
+// the down matrices side by side along k adds the weighted sum of the chosen experts.  Blocks with blockIdx.y ==
+// experts add the identity experts' share, weight * h, into the stream.
+template <typename T>
+__global__ void __launch_bounds__(256) expert_dense_weigh_kernel(T* __restrict__ z, const int* __restrict__ ids,
+                                                                 const float* __restrict__ weights, const T* __restrict__ h,
+                                                                 long long ld_h, float* __restrict__ x, int top, int experts,
+                                                                 int width, int ff) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, e = blockIdx.y;
+  if (e == experts) {
+    float w = 0.0f;
+    bool any = false;
+    for (int k = 0; k < top; ++k) {
+      const int id = ids[t * top + k];
+      if (id >= experts) { w += weights[t * top + k]; any = true; }
+    }
+    if (!any) return;
+    for (int n = threadIdx.x; n < width; n += blockDim.x) x[(size_t)t * width + n] += w * to_float<T>(h[(size_t)t * ld_h + n]);
+    return;
+  }
+  float w = 0.0f;
+  bool chosen = false;
+  for (int k = 0; k < top; ++k)
+    if (ids[t * top + k] == e) { w = weights[t * top + k]; chosen = true; }
+  T* row = z + ((size_t)t * experts + e) * ff;
+  if (!chosen) {
+    for (int j = threadIdx.x; j < ff; j += blockDim.x) row[j] = from_float<T>(0.0f);
+    return;
+  }
+  for (int j = threadIdx.x; j < ff; j += blockDim.x) {
+    const float p = fmaxf(to_float<T>(row[j]), 0.0f);
+    row[j] = from_float<T>(w * p * p);
+  }
+}
+
 }  // namespace
 
 // logits float32 [tokens, ld]; correction float32 [outputs] or null; ids int32 [tokens, top]; weights float32 [tokens, top].
@@ -314,11 +356,12 @@ TGE_API int tge_activation(void* rows, long long ld, int count, int width, int k
   return tge_launched("activation", 1);
 }
 
-// The direct path.  h: run dtype [tokens, >= width] with row stride ld_h; w_up [experts, ff, width], w_down [experts,
-// width, ff]; inner: run dtype scratch [tokens * top, ff]; x: the float32 stream [tokens, width].
-TGE_API int tge_experts_direct(const void* h, long long ld_h, const void* w_up, const void* w_down, const int* ids,
-                               const float* weights, void* inner, float* x, int tokens, int top, int experts, int width,
-                               int ff, int is_bf16, cudaStream_t stream) {
+// The direct path.  h: run dtype [tokens, >= width] with row stride ld_h; w_up [experts, ff, width]; row n of expert
+// e's down matrix (ff numbers) starts at w_down + e * down_expert + n * down_row; inner: run dtype scratch
+// [tokens * top, ff]; x: the float32 stream [tokens, width].
+TGE_API int tge_experts_direct(const void* h, long long ld_h, const void* w_up, const void* w_down, long long down_expert,
+                               long long down_row, const int* ids, const float* weights, void* inner, float* x, int tokens,
+                               int top, int experts, int width, int ff, int is_bf16, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && top > 0 && experts >= 0 && width > 0 && ff > 0, "experts: bad shape");
   if (tokens == 0) return 0;
   const int up_y = (ff + 7) / 8 < 64 ? (ff + 7) / 8 : 64;
@@ -327,12 +370,13 @@ TGE_API int tge_experts_direct(const void* h, long long ld_h, const void* w_up, 
     tge_launch(expert_up_kernel<__nv_bfloat16>, dim3(tokens * top, up_y), dim3(256), 0, stream, (const __nv_bfloat16*)h, ld_h,
                (const __nv_bfloat16*)w_up, ids, (__nv_bfloat16*)inner, top, experts, width, ff);
     tge_launch(expert_down_add_kernel<__nv_bfloat16>, dim3(tokens, down_y), dim3(256), 0, stream, (const __nv_bfloat16*)inner,
-               (const __nv_bfloat16*)w_down, (const __nv_bfloat16*)h, ld_h, ids, weights, x, top, experts, width, ff);
+               (const __nv_bfloat16*)w_down, (const __nv_bfloat16*)h, ld_h, ids, weights, x, top, experts, width, ff, down_expert,
+               down_row);
   } else {
     tge_launch(expert_up_kernel<float>, dim3(tokens * top, up_y), dim3(256), 0, stream, (const float*)h, ld_h,
                (const float*)w_up, ids, (float*)inner, top, experts, width, ff);
     tge_launch(expert_down_add_kernel<float>, dim3(tokens, down_y), dim3(256), 0, stream, (const float*)inner,
-               (const float*)w_down, (const float*)h, ld_h, ids, weights, x, top, experts, width, ff);
+               (const float*)w_down, (const float*)h, ld_h, ids, weights, x, top, experts, width, ff, down_expert, down_row);
   }
   return tge_launched("experts_direct", 2);
 }
@@ -367,4 +411,18 @@ TGE_API int tge_experts_combine_add(const float* outputs, const int* place, cons
     tge_launch(expert_combine_add_kernel<float>, dim3(tokens, chunks), dim3(256), 0, stream, outputs, place, weights,
                (const float*)h, ld_h, x, top, width);
   return tge_launched("experts_combine_add", 1);
+}
+
+// The dense path: z run dtype [tokens, experts * ff] in place (see the kernel); x float32 [tokens, width].
+TGE_API int tge_experts_dense_weigh(void* z, const int* ids, const float* weights, const void* h, long long ld_h, float* x,
+                                    int tokens, int top, int experts, int width, int ff, int is_bf16, cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && top > 0 && experts > 0 && experts < 65535 && width > 0 && ff > 0, "experts: bad shape");
+  if (tokens == 0) return 0;
+  if (is_bf16)
+    tge_launch(expert_dense_weigh_kernel<__nv_bfloat16>, dim3(tokens, experts + 1), dim3(256), 0, stream, (__nv_bfloat16*)z, ids,
+               weights, (const __nv_bfloat16*)h, ld_h, x, top, experts, width, ff);
+  else
+    tge_launch(expert_dense_weigh_kernel<float>, dim3(tokens, experts + 1), dim3(256), 0, stream, (float*)z, ids, weights,
+               (const float*)h, ld_h, x, top, experts, width, ff);
+  return tge_launched("experts_dense_weigh", 1);
 }

@@ -93,11 +93,14 @@ class DecoderModel:
             if layer.weights_from is None:
                 block.loaded()
 
-    def step_param_bytes(self) -> int:
-        """Bytes of parameters one step reads: every part once per visit, the embedding rows not counted."""
+    def step_param_bytes(self, tokens: int = 1) -> int:
+        """Bytes of parameters a step of ``tokens`` tokens reads: every part once per visit (a part whose share grows
+        with the tokens says so through ``step_param_bytes``), the embedding rows not counted."""
         total = self.final_norm.param_bytes() + self.head.param_bytes()
         for index in self.spec.schedule:
-            total += sum(part.param_bytes() for part in self.blocks[index].parts().values())
+            for part in self.blocks[index].parts().values():
+                grows = getattr(part, "step_param_bytes", None)
+                total += grows(tokens) if grows is not None else part.param_bytes()
         return total
 
     # -- cache ----------------------------------------------------------------

@@ -108,12 +108,19 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_head_linear", [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_int, _c_ll, _c_int,
                                           _c_int, _c_int, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_rotate_interleaved", [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int,
-                                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+                                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_latent_gather", [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                            _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_latent_scatter", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                                             _c_int, _c_ptr])
+        _declare(lib, "tge_gate_rows", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_router_topk", [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
                                           _c_ptr])
         _declare(lib, "tge_activation", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr])
-        _declare(lib, "tge_experts_direct", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
-                                             _c_int, _c_int, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_experts_direct", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_experts_dense_weigh", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int,
+                                                  _c_int, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_experts_group", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                             _c_int, _c_ptr])
         _declare(lib, "tge_experts_combine_add", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int,
@@ -1289,10 +1296,10 @@ def head_linear(x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor
 
 
 def rotate_interleaved(src: torch.Tensor, src_head: int, dst: torch.Tensor, dst_head: int, heads: int, width: int,
-                       cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor) -> torch.Tensor:
-    """dst[t, n * dst_head + e] = src[t, n * src_head + e] for e < width, with the first ``rot_dims`` numbers of every
-    run rotated in neighbouring pairs: (u, v) at position p -> (u cos a - v sin a, v cos a + u sin a), a = p * f_i,
-    from float32 tables [positions, rot_dims / 2].  Two buffers (or disjoint runs)."""
+                       cos: torch.Tensor, sin: torch.Tensor, rot_dims: int, positions: torch.Tensor, first: int = 0) -> torch.Tensor:
+    """dst[t, n * dst_head + e] = src[t, n * src_head + e] for e < width, with the ``rot_dims`` numbers of every
+    run from ``first`` on rotated in neighbouring pairs: (u, v) at position p -> (u cos a - v sin a, v cos a + u sin a),
+    a = p * f_i, from float32 tables [positions, rot_dims / 2].  Two buffers (or disjoint runs)."""
     _want(src, "rotation input", _FLOAT, contiguous=False)
     _want(dst, "rotation output", src.dtype, contiguous=False)
     _want(positions, "positions", torch.int32)
@@ -1308,9 +1315,65 @@ def rotate_interleaved(src: torch.Tensor, src_head: int, dst: torch.Tensor, dst_
     lib = core()
     _check(lib.tge_rotate_interleaved(src.data_ptr(), lds, int(src_head), dst.data_ptr(), ldd, int(dst_head), _ptr(cos) if rot_dims else None,
                                       _ptr(sin) if rot_dims else None, int(rot_dims), cos.shape[0] if rot_dims else 2 ** 31 - 1,
-                                      positions.data_ptr(), tokens, int(heads), int(width), int(src.dtype == torch.bfloat16),
-                                      status_word().data_ptr(), _stream()), lib)
+                                      positions.data_ptr(), tokens, int(heads), int(width), int(first),
+                                      int(src.dtype == torch.bfloat16), status_word().data_ptr(), _stream()), lib)
     return dst
+
+
+def latent_gather(pages: torch.Tensor, table: torch.Tensor, page_seq: torch.Tensor, page_idx: torch.Tensor, ctx_len: torch.Tensor,
+                  kv_rank: int, heads: int, latents: torch.Tensor, keys: torch.Tensor) -> None:
+    """For attention with every head's own keys over a latent cache: fills the step's own pages.  ``pages`` [pool, 1,
+    page, kv_rank + rot] found through ``table`` [S, max_pages]; own page p is request ``page_seq[p]``'s
+    ``page_idx[p]``-th; ``ctx_len`` [S] positions held.  latents [>= own pages * page, kv_rank] gets every position's
+    latent (zeros beyond what is held), keys [>= own pages, heads, page, per] the shared key part in the last rot
+    numbers of every head's row."""
+    _want(pages, "latent pages", _FLOAT)
+    _want(latents, "latent rows", pages.dtype)
+    _want(keys, "key pages", pages.dtype)
+    for name, t in (("block table", table), ("page owners", page_seq), ("page indices", page_idx), ("context lengths", ctx_len)):
+        _want(t, name, torch.int32)
+    num_pages, one, page_size, entry = pages.shape
+    own = page_seq.numel()
+    per = keys.shape[3]
+    if (one != 1 or keys.shape[0] < own or tuple(keys.shape[1:3]) != (heads, page_size) or latents.shape[1] != kv_rank
+            or latents.shape[0] < own * page_size or per < entry - kv_rank or page_idx.numel() != own):
+        raise KernelError("latent_gather: shapes do not agree")
+    lib = core()
+    _check(lib.tge_latent_gather(pages.data_ptr(), table.data_ptr(), table.shape[1], num_pages, page_seq.data_ptr(),
+                                 page_idx.data_ptr(), ctx_len.data_ptr(), own, page_size, int(kv_rank), entry - int(kv_rank),
+                                 int(heads), per, latents.data_ptr(), keys.data_ptr(), int(pages.dtype == torch.bfloat16),
+                                 status_word().data_ptr(), _stream()), lib)
+
+
+def latent_scatter(expanded: torch.Tensor, own_pages: int, dim: int, keys: torch.Tensor, values: torch.Tensor) -> None:
+    """expanded [own pages * page, heads * dim + heads * vdim] (per position every head's plain key part, then every
+    head's value) into keys [>= own pages, heads, page, per] (the first dim numbers of a row) and values [>= own
+    pages, heads, page, vdim]."""
+    _want(expanded, "expanded rows", _FLOAT, contiguous=False)
+    _want(keys, "key pages", expanded.dtype)
+    _want(values, "value pages", expanded.dtype)
+    _, heads, page_size, per = keys.shape
+    vdim = values.shape[3]
+    if (expanded.shape[0] < own_pages * page_size or expanded.shape[1] != heads * (dim + vdim) or keys.shape[0] < own_pages
+            or tuple(values.shape[:3]) != tuple(keys.shape[:3]) or per < dim):
+        raise KernelError("latent_scatter: shapes do not agree")
+    lib = core()
+    _check(lib.tge_latent_scatter(expanded.data_ptr(), _rows_2d(expanded, "expanded rows"), int(own_pages), page_size, heads,
+                                  int(dim), per, vdim, keys.data_ptr(), values.data_ptr(), int(expanded.dtype == torch.bfloat16),
+                                  _stream()), lib)
+
+
+def gate_rows(x: torch.Tensor, gate: torch.Tensor, heads: int, mode: int) -> torch.Tensor:
+    """In place: x[t, n, j] *= gate[t, n] (mode 1, gate float32 [T, heads]) or gate[t, n, j] (mode 2, [T, heads * vdim])."""
+    _want(x, "attended rows", _FLOAT, contiguous=False)
+    _want(gate, "gate", torch.float32)
+    tokens, width = x.shape
+    if width % heads or gate.shape[0] != tokens or gate.shape[1] != (heads if mode == 1 else width):
+        raise KernelError("gate_rows: shapes do not agree")
+    lib = core()
+    _check(lib.tge_gate_rows(x.data_ptr(), _rows_2d(x, "attended rows"), gate.data_ptr(), gate.shape[1], int(mode), tokens,
+                             int(heads), width // heads, int(x.dtype == torch.bfloat16), _stream()), lib)
+    return x
 
 
 # ----------------------------------------------------------------------------
@@ -1359,7 +1422,7 @@ def experts_direct(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, id
                    x: torch.Tensor) -> None:
     """x[t] += sum_k weights[t, k] * (w_down[e] relu(w_up[e] h[t])^2 with e = ids[t, k], or h[t] itself when e is
     beyond the experts), every pair reading its expert's rows directly: for steps of few tokens.  w_up [experts, ff,
-    width], w_down [experts, width, ff], x float32 [T, width]."""
+    width], w_down [width, experts, ff] (the experts' down matrices side by side), x float32 [T, width]."""
     _want(h, "expert input", _FLOAT, contiguous=False)
     _want(w_up, "expert up weights", h.dtype)
     _want(w_down, "expert down weights", h.dtype)
@@ -1369,13 +1432,33 @@ def experts_direct(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, id
     tokens, width = x.shape
     experts, ff = w_up.shape[0], w_up.shape[1]
     top = ids.shape[1]
-    if w_up.shape[2] != width or tuple(w_down.shape) != (experts, width, ff) or h.shape[0] != tokens or h.shape[1] != width:
+    if w_up.shape[2] != width or tuple(w_down.shape) != (width, experts, ff) or h.shape[0] != tokens or h.shape[1] != width:
         raise KernelError("experts: shapes do not agree")
     inner = torch.empty((tokens * top, ff), dtype=h.dtype, device=h.device)
     lib = core()
-    _check(lib.tge_experts_direct(h.data_ptr(), _rows_2d(h, "expert input"), w_up.data_ptr(), w_down.data_ptr(), ids.data_ptr(),
-                                  weights.data_ptr(), inner.data_ptr(), x.data_ptr(), tokens, top, experts, width, ff,
-                                  int(h.dtype == torch.bfloat16), _stream()), lib)
+    _check(lib.tge_experts_direct(h.data_ptr(), _rows_2d(h, "expert input"), w_up.data_ptr(), w_down.data_ptr(), ff,
+                                  experts * ff, ids.data_ptr(), weights.data_ptr(), inner.data_ptr(), x.data_ptr(), tokens, top,
+                                  experts, width, ff, int(h.dtype == torch.bfloat16), _stream()), lib)
+
+
+def experts_dense_weigh(z: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, h: torch.Tensor, x: torch.Tensor,
+                        experts: int) -> torch.Tensor:
+    """In place on z [T, experts * ff] (every expert's up projection of every token): the rows of a token's chosen
+    experts become weights[t, k] * relu(z)^2, all others zero; the share of choices beyond the experts (identity
+    experts), weights[t, k] * h[t], is added into x (float32 [T, width]).  Returns z."""
+    _want(z, "expert rows", _FLOAT)
+    _want(h, "expert input", z.dtype, contiguous=False)
+    _want(ids, "expert ids", torch.int32)
+    _want(weights, "expert weights", torch.float32)
+    _want(x, "stream", torch.float32)
+    tokens, width = x.shape
+    if z.shape[0] != tokens or z.shape[1] % experts or h.shape[0] != tokens or h.shape[1] != width or ids.shape[0] != tokens:
+        raise KernelError("experts: shapes do not agree")
+    lib = core()
+    _check(lib.tge_experts_dense_weigh(z.data_ptr(), ids.data_ptr(), weights.data_ptr(), h.data_ptr(), _rows_2d(h, "expert input"),
+                                       x.data_ptr(), tokens, ids.shape[1], int(experts), width, z.shape[1] // experts,
+                                       int(z.dtype == torch.bfloat16), _stream()), lib)
+    return z
 
 
 def experts_group(h: torch.Tensor, ids: torch.Tensor, experts: int):

@@ -14,7 +14,15 @@ s_ij = scale (q~_n . c_j + qr_n . kr_j), the paged attention kernels run with ON
 entries and whose values are the entries' first kv_rank numbers, and the attended latent returns through Wuv_n.  The
 kernels between the products: ``latent_prepare`` (both norms, rotation and store of the shared key part, gate),
 ``head_linear`` (the two per-head products, the second with the gate), ``rotate_interleaved`` (the queries'
-rotated part).  A layer may read another layer's entries (``LayerSpec.cache_from``; param ``shared_kv``): it then has
+rotated part).
+
+Long prompt portions go another way (``expand_keys``): there many queries meet every key, and attention with one
+key/value head of kv_rank + rot numbers costs more per pair than attention with every head's own keys of dim + rot
+and values of vdim.  So the latents of all positions the step's requests hold are gathered from the cache
+(``latent_gather``), one product with [Wuk; Wuv] gives every head's plain key parts and values, ``latent_scatter`` puts
+them into pages of the step's own beside the shared key part, and the ordinary paged attention runs with as many
+key/value heads as heads; the queries then need no Wuk and the attended rows no Wuv, only the gate (``gate_rows``).
+Both ways compute the same sums in another order.  A layer may read another layer's entries (``LayerSpec.cache_from``; param ``shared_kv``): it then has
 no Wdkv and stores nothing.
 
 **Token shift.**  ``shifted_mixer`` wraps any mixer: what the inner mixer reads is h_t + (h_(t-1) - h_t) * mu, element
@@ -31,12 +39,17 @@ from ..config.model_spec import PartSpec
 from .base import (MIXERS, POSITIONS, LayerCache, Mixer, PagedCacheSpec, ParamSpec, StateSpec, StepContext, build_part)
 
 
+_EXPANDED: Dict[tuple, tuple] = {}      # the steps' own key and value pages, per device and geometry
+
+
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     """params: ``hidden_size``, ``heads``, ``head_dim`` (plain query/key numbers per head), ``rope_dim`` (rotated
     ones), ``value_dim``, ``q_rank``, ``kv_rank``, ``scale``, ``eps`` (of the two latent norms), ``gate`` (``"none"``,
     ``"head"`` or ``"element"``), ``position`` (a PartSpec that offers ``pair_tables()``: the rotation of the rope_dim
-    part), ``shared_kv`` (bool: the entries are another layer's).
+    part), ``shared_kv`` (bool: the entries are another layer's), ``expand_keys`` (``"auto"``: every head's own keys
+    and values for steps with long portions, where the tensor-core attention takes the sizes; ``"never"``;
+    ``"always"``).
     weights: ``dq|uq|dkv|uk|uv|g|o.weight``, ``dq_norm.weight``, ``dkv_norm.weight`` (float32)."""
     graph_safe = True
 
@@ -54,6 +67,9 @@ class LatentAttention(Mixer):
         self.eps = float(p["eps"])
         self.gate = str(p.get("gate", "none"))
         self.shared_kv = bool(p.get("shared_kv", False))
+        self.expand_keys = str(p.get("expand_keys", "auto"))
+        if self.expand_keys not in ("auto", "never", "always"):
+            raise ValueError(f"latent_attention: expand_keys {self.expand_keys!r} is none of 'auto', 'never', 'always'")
         if min(self.hidden, self.heads, self.dim, self.vdim, self.q_rank, self.kv_rank) <= 0 or self.rot < 0:
             raise ValueError("latent_attention: sizes must be positive")
         if self.gate not in ("none", "head", "element"):
@@ -78,6 +94,7 @@ class LatentAttention(Mixer):
         self.w_uq: Optional[torch.Tensor] = None
         self.w_uk_t: Optional[torch.Tensor] = None      # [heads, kv_rank, dim]: queries into the latent space
         self.w_uv: Optional[torch.Tensor] = None        # [heads, vdim, kv_rank]: attended latents to values
+        self.w_ukv: Optional[torch.Tensor] = None       # rows [Wuk; Wuv]: latents to every head's keys and values
         self.w_o: Optional[torch.Tensor] = None
         self.q_norm_w: Optional[torch.Tensor] = None
         self.kv_norm_w: Optional[torch.Tensor] = None
@@ -110,6 +127,7 @@ class LatentAttention(Mixer):
         self.w_uq = tensors["uq.weight"].contiguous()
         self.w_uk_t = tensors["uk.weight"].view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = tensors["uv.weight"].view(self.heads, self.vdim, self.kv_rank).contiguous()
+        self.w_ukv = torch.cat([tensors["uk.weight"], tensors["uv.weight"]], dim=0).contiguous()
         self.w_o = tensors["o.weight"].contiguous()
 
     def flops(self, tokens: int, pairs: float) -> float:
@@ -135,6 +153,8 @@ class LatentAttention(Mixer):
                                             ctx.seq_of_token, table, pages if (own and cache.owner) else None, dtype)
         q = ops.linear(q_latent, self.w_uq, None, ops.GEMM_STORE)
         per_head = self.dim + self.rot
+        if self.expands(ctx, pages):
+            return self.attend_expanded(q, gate, ctx, pages, table, out)
         queries = torch.empty((tokens, self.heads * self.entry), dtype=dtype, device=h.device)
         ops.head_linear(q, per_head, self.w_uk_t, queries, self.entry)
         if self.rot:
@@ -148,6 +168,65 @@ class LatentAttention(Mixer):
             out = torch.empty((tokens, self.heads * self.vdim), dtype=dtype, device=h.device)
         mode = {"none": 0, "head": 1, "element": 2}[self.gate]
         return ops.head_linear(attended, self.kv_rank, self.w_uv, out, self.vdim, gate if mode else None, mode)
+
+    def expands(self, ctx: StepContext, pages: torch.Tensor) -> bool:
+        """Whether this step gives every head its own keys and values: long portions that between them bring a fair
+        share of the positions whose keys they read (each position's keys cost a product row; each query-key pair
+        saves a little)."""
+        if self.expand_keys == "never" or not ctx.host_q_lens or len(ctx.host_start_pos) != len(ctx.host_q_lens):
+            return False
+        if self.expand_keys == "always":
+            return True
+        held = sum(s + n for s, n in zip(ctx.host_start_pos, ctx.host_q_lens))
+        return (self.env.dtype == torch.bfloat16 and ctx.max_q_len >= 32 and held <= 16 * ctx.num_tokens
+                and self.ops.mma_attention_supports(self.dim + self.rot, self.heads, self.heads, pages.shape[2], self.vdim))
+
+    def own_pages(self, ctx: StepContext, page_size: int, device):
+        """The step's own pages, one run per request: (page owners, page indices, block table [S, most], count); made
+        once per step and shared by the model's layers of this kind."""
+        key = ("latent_own_pages", page_size)
+        if key not in ctx.scratch:
+            counts = [-(-(s + n) // page_size) for s, n in zip(ctx.host_start_pos, ctx.host_q_lens)]
+            most = max(counts)
+            owners, indices, rows, first = [], [], [], 0
+            for seq, count in enumerate(counts):
+                owners += [seq] * count
+                indices += list(range(count))
+                rows.append(list(range(first, first + count)) + [-1] * (most - count))
+                first += count
+            make = lambda values: torch.tensor(values, dtype=torch.int32).to(device, non_blocking=True)
+            ctx.scratch[key] = (make(owners), make(indices), make(rows), first)
+        return ctx.scratch[key]
+
+    def attend_expanded(self, q: torch.Tensor, gate, ctx: StepContext, pages: torch.Tensor, table: torch.Tensor,
+                        out: Optional[torch.Tensor]) -> torch.Tensor:
+        ops = self.ops
+        dtype, device = self.env.dtype, q.device
+        page_size = pages.shape[2]
+        per = self.dim + self.rot
+        owners, indices, own_table, count = self.own_pages(ctx, page_size, device)
+        # buffers that only grow, shared by all layers of these sizes: the attention kernels keep one descriptor per
+        # (address, geometry) of a page pool
+        held = _EXPANDED.get((device, self.heads, page_size, per, self.vdim, dtype))
+        if held is None or held[0].shape[0] < count:
+            room = max(count, 2 * held[0].shape[0] if held is not None else 0)
+            held = (torch.zeros((room, self.heads, page_size, per), dtype=dtype, device=device),
+                    torch.zeros((room, self.heads, page_size, self.vdim), dtype=dtype, device=device))
+            _EXPANDED[(device, self.heads, page_size, per, self.vdim, dtype)] = held
+        keys, values = held
+        latents = torch.empty((count * page_size, self.kv_rank), dtype=dtype, device=device)
+        ops.latent_gather(pages, table, owners, indices, ctx.ctx_len, self.kv_rank, self.heads, latents, keys)
+        expanded = ops.linear(latents, self.w_ukv, None, ops.GEMM_STORE)
+        ops.latent_scatter(expanded, count, self.dim, keys, values)
+        queries = torch.empty_like(q)
+        ops.rotate_interleaved(q, per, queries, per, self.heads, per, self.cos, self.sin, self.rot_dims, ctx.positions,
+                               first=self.dim)
+        attended = ops.attention(queries, keys, values, own_table, ctx.q_start, ctx.start_pos, ctx.positions, ctx.seq_of_token,
+                                 ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads, self.heads, per, self.scale,
+                                 split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
+                                 decode_prefix=ctx.decode_prefix, out=out)
+        mode = {"none": 0, "head": 1, "element": 2}[self.gate]
+        return ops.gate_rows(attended, gate, self.heads, mode) if mode else attended
 
     def inner(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None):
         return self.attend(h, ctx, cache, out=out)

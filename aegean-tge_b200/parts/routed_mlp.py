@@ -12,11 +12,18 @@ The correction steers the choice only; the weights use the plain scores.  Identi
 router outputs and have no tensors.  The sum over a token's choices is formed in float32 in the order of the choice
 and added into the float32 stream.
 
-Two ways through the experts.  A step of few tokens (every decode step) lets each (token, choice) pair read its
-expert's rows directly (``experts_direct``: two kernels, nothing read from the host, so it can be captured into a
-CUDA graph).  A step of many tokens groups the pairs by expert and runs one ordinary product per expert and
-projection over that expert's block of rows (``experts_group`` -> products -> ``experts_combine_add``); the host reads
-the group sizes, which a step with prompt portions may do.
+Three ways through the experts.  A step of very few tokens lets each (token, choice) pair read its expert's rows
+directly (``experts_direct``: two kernels).  A step of some tokens whose choices between them reach most experts
+anyway (a decode batch, a short portion: at least twice as many pairs as experts, at most ``DENSE_MAX_TOKENS``
+tokens) goes through ALL experts: one product of the tokens with every up matrix, ``experts_dense_weigh`` (the
+chosen experts' activated rows times their weights, zeros elsewhere), one product with the down matrices side by
+side along k that adds into the stream; every expert's weights cross the memory bus once, on the tensor cores, and
+the work wasted on zeros is free while the step is bound by those bytes.  Neither reads anything from the host, so
+both can be captured into a CUDA graph.  A step of many tokens groups the pairs by expert and runs one ordinary product per
+expert and projection over that expert's block of rows (``experts_group`` -> products ->
+``experts_combine_add``); the host reads the group sizes, which a step with prompt portions may do.
+
+The down matrices are kept side by side, [hidden, experts, inner]: expert e's matrix is the strided view [:, e, :].
 """
 from __future__ import annotations
 
@@ -26,7 +33,8 @@ import torch
 
 from .base import FEED_FORWARDS, FeedForward, ParamSpec, StepContext
 
-DIRECT_MAX_TOKENS = 32      # steps of up to this many tokens (and every step of single tokens) take the direct path
+DIRECT_MAX_TOKENS = 32      # steps of up to this many tokens (and every step of single tokens) avoid the grouped path
+DENSE_MAX_TOKENS = 256      # beyond this many tokens the wasted products of the dense path would cost more than its bytes
 
 
 @FEED_FORWARDS.register("routed_experts")
@@ -65,7 +73,7 @@ class RoutedExperts(FeedForward):
         self.w_router: Optional[torch.Tensor] = None
         self.correction: Optional[torch.Tensor] = None
         self.w_up: Optional[torch.Tensor] = None         # [experts, inner, hidden]
-        self.w_down: Optional[torch.Tensor] = None       # [experts, hidden, inner]
+        self.w_down: Optional[torch.Tensor] = None       # [hidden, experts, inner]
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs = {"router.weight": ParamSpec((self.outputs, self.hidden))}
@@ -81,15 +89,26 @@ class RoutedExperts(FeedForward):
         self.correction = tensors["correction"].contiguous() if self.has_correction else None
         if self.experts:
             self.w_up = torch.stack([tensors[f"experts.{e}.up.weight"] for e in range(self.experts)]).contiguous()
-            self.w_down = torch.stack([tensors[f"experts.{e}.down.weight"] for e in range(self.experts)]).contiguous()
+            self.w_down = torch.stack([tensors[f"experts.{e}.down.weight"] for e in range(self.experts)], dim=1).contiguous()
         else:
             self.w_up = torch.empty((0, self.inner_size, self.hidden), dtype=self.w_router.dtype, device=self.w_router.device)
-            self.w_down = torch.empty((0, self.hidden, self.inner_size), dtype=self.w_router.dtype, device=self.w_router.device)
+            self.w_down = torch.empty((self.hidden, 0, self.inner_size), dtype=self.w_router.dtype, device=self.w_router.device)
 
     def param_bytes(self) -> int:
         """What one token's step reads: the router and the chosen experts (a large batch touches more of them)."""
         item = self.env.dtype.itemsize
         return (self.outputs * self.hidden + min(self.top, self.experts) * 2 * self.inner_size * self.hidden) * item + 4 * self.outputs
+
+    def dense(self, tokens: int) -> bool:
+        """Whether a step of this many tokens runs all experts (its choices reach most of them anyway)."""
+        return bool(self.experts) and 2 * self.experts <= tokens * self.top and tokens <= DENSE_MAX_TOKENS
+
+    def step_param_bytes(self, tokens: int) -> int:
+        """What a step of ``tokens`` tokens reads: the router, and all experts on the dense path, else as many as
+        uniform choices would reach on average."""
+        item = self.env.dtype.itemsize
+        reached = self.experts if self.dense(tokens) else self.experts * (1.0 - (1.0 - min(self.top / self.outputs, 1.0)) ** tokens)
+        return int((self.outputs * self.hidden + reached * 2 * self.inner_size * self.hidden) * item) + 4 * self.outputs
 
     def flops(self, tokens: int, pairs: float) -> float:
         return 2.0 * tokens * (self.outputs * self.hidden + self.top * 2 * self.inner_size * self.hidden)
@@ -107,7 +126,13 @@ class RoutedExperts(FeedForward):
         ops = self.ops
         h, ids, weights = self.route(h)
         tokens = h.shape[0]
-        if ctx.max_q_len <= 1 or tokens <= DIRECT_MAX_TOKENS or self.experts == 0:
+        few = ctx.max_q_len <= 1 or tokens <= DIRECT_MAX_TOKENS
+        if self.dense(tokens):
+            z = ops.linear(h, self.w_up.view(self.experts * self.inner_size, self.hidden), None, ops.GEMM_STORE)
+            ops.experts_dense_weigh(z, ids, weights, h, x, self.experts)
+            ops.linear(z, self.w_down.view(self.hidden, self.experts * self.inner_size), None, ops.GEMM_ADD_F32, out=x)
+            return None
+        if few or self.experts == 0:
             ops.experts_direct(h, self.w_up, self.w_down, ids, weights, x)
             return None
         place, offsets, grouped = ops.experts_group(h, ids, self.experts)
@@ -124,7 +149,7 @@ class RoutedExperts(FeedForward):
         for e in range(self.experts):
             lo, hi = bounds[e], bounds[e + 1]
             if hi > lo:
-                ops.linear(inner[lo:hi], self.w_down[e], None, ops.GEMM_STORE_F32, out=outputs[lo:hi])
+                ops.linear(inner[lo:hi], self.w_down[:, e, :], None, ops.GEMM_STORE_F32, out=outputs[lo:hi])
         ops.experts_combine_add(outputs, place, weights, h, x)
         return None
 
