@@ -308,6 +308,8 @@ def compare_designs(configs: Dict[str, dict], prompt_len: int = 2048, batches=(8
                                   "share": round(r["share"], 4)} for r in rows[:12] + rows[-1:]]
             row["prefill_kernels"] = keep(step_timeline(engine, 1, prompt_len, prefill=True))
             row["decode_kernels"] = keep(step_timeline(engine, batches[0], prompt_len, prefill=False))
+            if len(batches) > 1:
+                row[f"decode_kernels_b{batches[-1]}"] = keep(step_timeline(engine, batches[-1], prompt_len, prefill=False))
         out[name] = row
         del engine
     return out

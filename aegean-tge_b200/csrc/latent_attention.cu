@@ -170,6 +170,38 @@ __global__ void __launch_bounds__(256) rotate_interleaved_kernel(
   }
 }
 
+// The same on pairs of bfloat16 (every size, stride and the first rotated place even, rows on 4 bytes): a thread owns
+// one pair, so a rotated pair is read once.
+__global__ void __launch_bounds__(256) rotate_interleaved_pairs_kernel(
+    const __nv_bfloat16* __restrict__ src, long long src_row, long long src_head, __nv_bfloat16* __restrict__ dst,
+    long long dst_row, long long dst_head, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+    int rot_dims, int max_positions, const int* __restrict__ positions, int tokens, int heads, int width, int first,
+    int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int half = width >> 1;
+  const long long per_token = (long long)heads * half;
+  const long long total = (long long)tokens * per_token;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / per_token);
+    const int rest = (int)(idx - (long long)t * per_token);
+    const int head = rest / half;
+    const int e = 2 * (rest - head * half);
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_positions) {
+      atomicOr(status, TGE_STATUS_BAD_ROW);
+      continue;
+    }
+    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + (size_t)t * src_row + (size_t)head * src_head + e));
+    if (e >= first && e < first + rot_dims) {
+      const int pair = (e - first) >> 1;
+      const float c = cos_table[(size_t)pos * (rot_dims / 2) + pair], s = sin_table[(size_t)pos * (rot_dims / 2) + pair];
+      v = make_float2(fmaf(v.x, c, -v.y * s), fmaf(v.y, c, v.x * s));
+    }
+    *reinterpret_cast<__nv_bfloat162*>(dst + (size_t)t * dst_row + (size_t)head * dst_head + e) = __floats2bfloat162_rn(v.x, v.y);
+  }
+}
+
 // One block per position slot of the step's own pages: slot r = page * page_size + offset; page p belongs to request
 // page_seq[p] and is its page_idx[p]-th.  Positions beyond what the request holds give zeros.
 template <typename T>
@@ -297,6 +329,13 @@ TGE_API int tge_rotate_interleaved(const void* src, long long src_row, long long
   if (tokens == 0) return 0;
   const long long total = (long long)tokens * heads * width;
   const int blocks = (int)((total + 255) / 256 > 65535 * 16 ? 65535 * 16 : (total + 255) / 256);
+  if (is_bf16 && ((width | first | src_row | src_head | dst_row | dst_head) & 1) == 0 && (((uintptr_t)src | (uintptr_t)dst) & 3) == 0) {
+    const int pair_blocks = (int)((total / 2 + 255) / 256 > 148 * 16 ? 148 * 16 : (total / 2 + 255) / 256);
+    tge_launch(rotate_interleaved_pairs_kernel, dim3(pair_blocks), dim3(256), 0, stream, (const __nv_bfloat16*)src, src_row,
+               src_head, (__nv_bfloat16*)dst, dst_row, dst_head, cos_table, sin_table, rot_dims, max_positions, positions, tokens,
+               heads, width, first, status);
+    return tge_launched("rotate_interleaved", 1);
+  }
   if (is_bf16)
     tge_launch(rotate_interleaved_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)src,
                src_row, src_head, (__nv_bfloat16*)dst, dst_row, dst_head, cos_table, sin_table, rot_dims, max_positions,

@@ -18,7 +18,8 @@ namespace {
 template <typename TO>
 __global__ void __launch_bounds__(256) group_norm_kernel(const float* x, const float* __restrict__ weight,
                                                          const int* __restrict__ rows, TO* out, int src_rows, int width,
-                                                         int groups, float eps, int* status) {
+                                                         int groups, float eps, int* status,
+                                                         const float* __restrict__ weight2, TO* out2) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -37,8 +38,18 @@ __global__ void __launch_bounds__(256) group_norm_kernel(const float* x, const f
     for (int i = threadIdx.x; i < size; i += blockDim.x) ss = fmaf(part[i], part[i], ss);
     ss = block_sum(ss, scratch);                     // every read of the part is done once this returns
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
-    for (int i = threadIdx.x; i < size; i += blockDim.x)
-      dst[(size_t)g * size + i] = from_float<TO>(part[i] * inv * weight[(size_t)g * size + i]);
+    if (out2 == nullptr) {
+      for (int i = threadIdx.x; i < size; i += blockDim.x)
+        dst[(size_t)g * size + i] = from_float<TO>(part[i] * inv * weight[(size_t)g * size + i]);
+    } else {
+      // a second norm of the same rows (same groups and eps, another weight): the statistics serve both
+      TO* dst2 = out2 + (size_t)r * width;
+      for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = part[i] * inv;
+        dst[(size_t)g * size + i] = from_float<TO>(v * weight[(size_t)g * size + i]);
+        dst2[(size_t)g * size + i] = from_float<TO>(v * weight2[(size_t)g * size + i]);
+      }
+    }
   }
 }
 
@@ -91,9 +102,12 @@ __global__ void __launch_bounds__(256) shift_state_update_kernel(const T* __rest
 }  // namespace
 
 // x float32 [src_rows, width]; rows: null or int32 [out_rows]; out: float32 (out_kind 0; may be x itself when rows is
-// null) or bfloat16 (out_kind 1), [out_rows, width].
+// null) or bfloat16 (out_kind 1), [out_rows, width].  weight2 / out2: null, or a second weight and output like the first.
 TGE_API int tge_group_norm(const float* x, const float* weight, const int* rows, void* out, int out_kind, int out_rows,
-                           int src_rows, int width, int groups, float eps, int* status, cudaStream_t stream) {
+                           int src_rows, int width, int groups, float eps, const float* weight2, void* out2, int* status,
+                           cudaStream_t stream) {
+  TGE_REQUIRE((weight2 == nullptr) == (out2 == nullptr) && (out2 == nullptr || (out2 != out && out2 != (void*)x && out != (void*)x)),
+              "group_norm: a second output needs a second weight and buffers of its own");
   TGE_REQUIRE(out_rows >= 0 && src_rows >= 0 && width > 0, "group_norm: bad shape");
   TGE_REQUIRE(groups > 0 && width % groups == 0, "group_norm: %d groups do not divide a row of %d", groups, width);
   TGE_REQUIRE(eps > 0.0f, "group_norm: eps must be positive");
@@ -101,10 +115,10 @@ TGE_API int tge_group_norm(const float* x, const float* weight, const int* rows,
   if (out_rows == 0) return 0;
   if (out_kind == 0)
     tge_launch(group_norm_kernel<float>, dim3(out_rows), dim3(256), 0, stream, x, weight, rows, (float*)out, src_rows,
-               width, groups, eps, status);
+               width, groups, eps, status, weight2, (float*)out2);
   else
     tge_launch(group_norm_kernel<__nv_bfloat16>, dim3(out_rows), dim3(256), 0, stream, x, weight, rows,
-               (__nv_bfloat16*)out, src_rows, width, groups, eps, status);
+               (__nv_bfloat16*)out, src_rows, width, groups, eps, status, weight2, (__nv_bfloat16*)out2);
   return tge_launched("group_norm", 1);
 }
 

@@ -99,7 +99,7 @@ def core() -> ctypes.CDLL:
                                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
                                                      _c_ptr])
         _declare(lib, "tge_group_norm", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                         _c_ptr, _c_ptr])
+                                         _c_ptr, _c_ptr, _c_ptr, _c_ptr])
         _declare(lib, "tge_token_shift", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                           _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_latent_prepare", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float,
@@ -1175,10 +1175,12 @@ def sample_cuts(scores: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
 # norms in groups, token shift
 # ----------------------------------------------------------------------------
 def group_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out_dtype: torch.dtype,
-               rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               weight2: Optional[torch.Tensor] = None):
     """RMS norm in ``groups`` equal consecutive parts of every float32 row (each part over its own root mean
     square), times ``weight``; rows optionally gathered by ``rows``.  ``out_dtype`` float32 or bfloat16; ``out`` may
-    be ``x`` itself (float32, no gather): the stream normalised in place."""
+    be ``x`` itself (float32, no gather): the stream normalised in place.  With ``weight2`` the same normalised rows
+    are also written times that weight, and the result is the pair of outputs."""
     _want(x, "norm input", torch.float32)
     _want(weight, "norm weight", torch.float32)
     src_rows, width = x.shape
@@ -1192,10 +1194,17 @@ def group_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, o
     _want(out, "norm output", _FLOAT)
     if tuple(out.shape) != (out_rows, width) or (out.data_ptr() == x.data_ptr() and (rows is not None or out.dtype != x.dtype)):
         raise KernelError("group_norm: the output must be [rows, width], and may be the input only ungathered in float32")
+    out2 = None
+    if weight2 is not None:
+        _want(weight2, "second norm weight", torch.float32)
+        if weight2.numel() != width or out.data_ptr() == x.data_ptr():
+            raise KernelError("group_norm: a second weight of the row's width, and not in place")
+        out2 = torch.empty_like(out)
     lib = core()
     _check(lib.tge_group_norm(x.data_ptr(), weight.data_ptr(), _ptr(rows), out.data_ptr(), int(out.dtype == torch.bfloat16),
-                              out_rows, src_rows, width, int(groups), float(eps), status_word().data_ptr(), _stream()), lib)
-    return out
+                              out_rows, src_rows, width, int(groups), float(eps), _ptr(weight2), _ptr(out2),
+                              status_word().data_ptr(), _stream()), lib)
+    return out if weight2 is None else (out, out2)
 
 
 def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, seq_of_token: torch.Tensor,

@@ -94,11 +94,16 @@ class ParallelBlock(Block):
 
     def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None, next_takes_deferred=False):
         ops = self.env.ops
-        if h is None:
-            h = self.mixer_norm.forward(x)
         # the feed-forward's rows: its own norm of the same x (taken before anything is added), else the mixer's
         own_rows = self.ffn_norm is not None and self.feed_forward is not None
-        b = self.ffn_norm.forward(x) if own_rows else h
+        both = getattr(self.mixer_norm, "forward_with", None) if (h is None and own_rows) else None
+        pair = both(self.ffn_norm, x) if both is not None else None       # two norms that share their statistics
+        if pair is not None:
+            h, b = pair
+        else:
+            if h is None:
+                h = self.mixer_norm.forward(x)
+            b = self.ffn_norm.forward(x) if own_rows else h
         if self.w_out is None:
             # whole sublayers, added one by one
             if isinstance(h, ops.DeferredRows):

@@ -134,7 +134,8 @@ class LatentAttention(Mixer):
         in_rows = self.q_rank + (0 if self.shared_kv else self.entry) + self.gate_n
         products = 2.0 * tokens * (in_rows * self.hidden + self.heads * (self.dim + self.rot) * self.q_rank
                                    + self.heads * self.kv_rank * (self.dim + self.vdim) + self.heads * self.vdim * self.hidden)
-        return products + 2.0 * self.heads * (self.entry + self.kv_rank) * pairs
+        # per query-key pair: every head's own keys and values (what long portions run) or the entries as one head
+        return products + 2.0 * self.heads * min(self.entry + self.kv_rank, self.dim + self.rot + self.vdim) * pairs
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         return PagedCacheSpec(entries=(("kv", (1, self.entry)),), window=None)

@@ -82,6 +82,14 @@ class GroupRMSNorm(Norm):
             raise RuntimeError("group_rmsnorm: the checkpoint holds no weight for this norm")
         return self.ops.group_norm(x, self.weight, self.eps, self.groups, self.env.dtype, rows=rows)
 
+    def forward_with(self, other: "GroupRMSNorm", x: torch.Tensor):
+        """This norm and ``other`` of the same rows, (mine, theirs), from one kernel when the two differ in their weights
+        only; else None."""
+        if (not isinstance(other, GroupRMSNorm) or other.groups != self.groups or other.eps != self.eps or other.size != self.size
+                or self.weight is None or other.weight is None):
+            return None
+        return self.ops.group_norm(x, self.weight, self.eps, self.groups, self.env.dtype, weight2=other.weight)
+
     def forward_stream(self, x: torch.Tensor) -> torch.Tensor:
         """The float32 rows normalised in place (a stream that starts from normalised embeddings)."""
         return self.ops.group_norm(x, self.weight, self.eps, self.groups, torch.float32, out=x)

@@ -240,6 +240,11 @@ def test_norm_in_groups(ops, dtype, width, groups):
     if groups > 1:
         whole = torch.from_numpy(plain.group_norm(x.numpy(), w.numpy(), 1, 1e-5))
         assert rel_error(got.float().cpu(), whole) > 0.1
+    # two norms of the same rows that differ in their weights only, from one launch
+    w2 = 1 + 0.2 * torch.randn(width, generator=gen)
+    first, second = ops.group_norm(x.to(DEV), w.to(DEV), 1e-5, groups, TORCH[dtype], weight2=w2.to(DEV))
+    assert torch.equal(first, got)
+    assert rel_error(second, torch.from_numpy(plain.group_norm(x.numpy(), w2.numpy(), groups, 1e-5))) < KERNEL_TOL[dtype]
     stream = x.to(DEV)
     assert ops.group_norm(stream, w.to(DEV), 1e-5, groups, torch.float32, out=stream).data_ptr() == stream.data_ptr()
     assert rel_error(stream, ref) < KERNEL_TOL["float32"]
@@ -312,6 +317,15 @@ def test_rotation_of_neighbouring_pairs(ops, dtype, heads, width, dims, base):
     assert rel_error(dst, ref) < KERNEL_TOL[dtype]
     if dims < width:
         assert torch.equal(dst.view(len(positions), heads, width)[:, :, dims:].cpu(), runs[:, :, dims:].to(TORCH[dtype]))
+    # the rotated numbers at the end of a run, the plain ones before them copied
+    if width > dims:
+        lead = width - dims
+        moved = torch.cat([runs[..., dims:], runs[..., :dims]], dim=-1).to(TORCH[dtype])
+        want = torch.cat([ref.view(len(positions), heads, width)[..., dims:], ref.view(len(positions), heads, width)[..., :dims]], dim=-1)
+        back = torch.zeros(len(positions), heads * width, dtype=TORCH[dtype], device=DEV)
+        ops.rotate_interleaved(moved.reshape(len(positions), -1).to(DEV), width, back, width, heads, width, cos.to(DEV), sin.to(DEV), dims,
+                               _i32(positions), first=lead)
+        assert rel_error(back, want.reshape(len(positions), -1)) < KERNEL_TOL[dtype]
     # the halves-paired rotation is another function: it must differ
     half = runs.clone()
     angle = torch.tensor(positions, dtype=torch.float64)[:, None] * base ** (-2.0 * torch.arange(dims // 2) / dims)
@@ -339,6 +353,15 @@ def test_two_parameter_activation(ops, dtype):
     squared = z.clone().to(DEV)
     ops.activation(squared, ops.ACT_RELU_SQUARED)
     assert rel_error(squared, z.double().clamp(min=0) ** 2) < KERNEL_TOL[dtype]
+    # rows of a multiple of eight numbers inside wider rows (eight at a time in bfloat16)
+    y = (torch.randn(9, 48, generator=gen) * 3).to(TORCH[dtype])
+    for kind, params, ref in ((ops.ACT_XIELU, torch.tensor([0.3, -0.7], device=DEV), plain.xielu(y.double().numpy(), 0.3, -0.7)),
+                              (ops.ACT_RELU_SQUARED, None, (y.double().clamp(min=0) ** 2).numpy())):
+        wide = torch.full((9, 64), 2.0, dtype=TORCH[dtype], device=DEV)
+        wide[:, :48] = y.to(DEV)
+        ops.activation(wide[:, :48], kind, params)
+        assert rel_error(wide[:, :48], torch.from_numpy(ref)) < KERNEL_TOL[dtype]
+        assert float((wide[:, 48:] - 2.0).abs().max()) == 0.0
 
 
 # ---------------------------------------------------------------------------
@@ -464,7 +487,7 @@ class _LatentCase:
     function on whole sequences beside it."""
 
     def __init__(self, dtype, hidden, heads, dim, rot, vdim, q_rank, kv_rank, scale, base, dims, gate, page_size=16, seed=0,
-                 matched=False):
+                 matched=False, expand="never"):
         from aegean_tge_b200 import ops
         from aegean_tge_b200.config import PartSpec
         from aegean_tge_b200.parts import MIXERS, build_part
@@ -476,7 +499,7 @@ class _LatentCase:
         self.env = BuildEnv(dtype=TORCH[dtype], device=DEV, hidden_size=hidden, max_positions=2048, page_size=page_size, ops=ops)
         position = PartSpec("rope_interleaved", {"head_dim": rot, "theta": base, "rotary_dim": dims})
         self.params = {"hidden_size": hidden, "heads": heads, "head_dim": dim, "rope_dim": rot, "value_dim": vdim, "q_rank": q_rank,
-                       "kv_rank": kv_rank, "scale": scale, "eps": 1e-5, "gate": gate, "position": position}
+                       "kv_rank": kv_rank, "scale": scale, "eps": 1e-5, "gate": gate, "position": position, "expand_keys": expand}
         locals_ = ["dq.weight", "dq_norm.weight", "uq.weight", "dkv.weight", "dkv_norm.weight", "uk.weight", "uv.weight", "o.weight"]
         if gate != "none":
             locals_.append("g.weight")
@@ -573,8 +596,11 @@ LATENT_CUTS = [[[70, 45]], [[40, 3], [2, 40], [28, 2]], [[1, 0], [1, 1], [2, 1],
 @pytest.mark.parametrize("shape", LATENT_SHAPES)
 @pytest.mark.parametrize("cuts", LATENT_CUTS)
 @pytest.mark.parametrize("page_size", [16, 64])
-def test_latent_attention_part_with_its_cache(dtype, shape, cuts, page_size):
-    case = _LatentCase(dtype, *shape, page_size=page_size, seed=len(cuts))
+@pytest.mark.parametrize("expand", ["never", "always"])
+def test_latent_attention_part_with_its_cache(dtype, shape, cuts, page_size, expand):
+    """``expand``: the entries serve as one key/value head, or every head gets its own keys and values in pages of the
+    step's own (what long portions do); the same function either way."""
+    case = _LatentCase(dtype, *shape, page_size=page_size, seed=len(cuts), expand=expand)
     assert case.part.cache_spec().entries == (("kv", (1, shape[6] + shape[3])),) and case.part.cache_spec().window is None
     gen = torch.Generator().manual_seed(11)
     lengths = [sum(step[r] for step in cuts) for r in range(2)]
@@ -611,11 +637,13 @@ def test_a_layer_that_reads_another_layers_entries(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("page_size", [16, 64])
 @pytest.mark.parametrize("tail", [0, 1, 40])
-def test_one_far_key_among_hundreds_stands_out(dtype, page_size, tail):
+@pytest.mark.parametrize("expand", ["auto", "always"])
+def test_one_far_key_among_hundreds_stands_out(dtype, page_size, tail, expand):
     """Queries and keys are made alike and the softmax sharp, so the last prompt token (or, with a tail, a token decoded
     alone after it) gives nearly all its weight to the one row made for it: the first token, a page's last or first
     entry, or a row hundreds of tokens back.  Without that row the output is another."""
-    case = _LatentCase(dtype, 96, 4, 32, 16, 48, 40, 40, 3.0, 5000.0, 16, "head", page_size=page_size, seed=3, matched=True)
+    case = _LatentCase(dtype, 96, 4, 32, 16, 48, 40, 40, 3.0, 5000.0, 16, "head", page_size=page_size, seed=3, matched=True,
+                       expand=expand)
     gen = torch.Generator().manual_seed(13)
     length = 600
     for place in (0, 1, page_size - 1, page_size, 63, 64, 65, 300, length - 3):
