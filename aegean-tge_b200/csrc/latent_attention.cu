@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(
 }
 
 constexpr int HL_BM = 32, HL_BN = 32, HL_BK = 32;
+constexpr int HL_ROWS_MAX_TOKENS = 16;     // steps of up to this many tokens take the kernel that walks the rows
 
 // out[t, n, j] = gate * sum_k x[t, n, k] * w[n, j, k]; a block owns 32 tokens x 32 outputs of one head, a thread a
 // 2 x 2 patch, every output accumulated over k in ascending order (so a row's result does not depend on the batch).
@@ -138,6 +139,43 @@ __global__ void __launch_bounds__(256) head_linear_kernel(
       if (gate_mode == 1) v *= gate[(size_t)t * gate_row + head];
       else if (gate_mode == 2) v *= gate[(size_t)t * gate_row + (size_t)head * n_out + j];
       out[(size_t)t * out_row + (size_t)head * out_head + j] = from_float<T>(v);
+    }
+  }
+}
+
+// The same product for a step of few tokens: a warp owns one output of one head and walks the tokens four at a time,
+// every lane the numbers lane, lane + 32, ... of the rows, the lanes' sums meeting in a butterfly; the order of a row's
+// sum depends on k_in alone.
+template <typename T>
+__global__ void __launch_bounds__(256) head_linear_rows_kernel(
+    const T* __restrict__ x, long long x_row, long long x_head, const T* __restrict__ w, T* __restrict__ out,
+    long long out_row, long long out_head, const float* __restrict__ gate, int gate_mode, long long gate_row, int tokens,
+    int n_out, int k_in) {
+  pdl_trigger();
+  pdl_wait();
+  const int head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.y * 8 + warp;
+  if (j >= n_out) return;
+  const T* wrow = w + ((size_t)head * n_out + j) * k_in;
+  for (int t0 = 0; t0 < tokens; t0 += 4) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k = lane; k < k_in; k += 32) {
+      const float wk = to_float<T>(wrow[k]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = t0 + i < tokens ? t0 + i : tokens - 1;
+        acc[i] = fmaf(to_float<T>(x[(size_t)t * x_row + (size_t)head * x_head + k]), wk, acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = warp_sum(acc[i]);
+      const int t = t0 + i;
+      if (lane == 0 && t < tokens) {
+        if (gate_mode == 1) v *= gate[(size_t)t * gate_row + head];
+        else if (gate_mode == 2) v *= gate[(size_t)t * gate_row + (size_t)head * n_out + j];
+        out[(size_t)t * out_row + (size_t)head * out_head + j] = from_float<T>(v);
+      }
     }
   }
 }
@@ -306,6 +344,16 @@ TGE_API int tge_head_linear(const void* x, long long x_row, long long x_head, co
   TGE_REQUIRE(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0 || gate != nullptr), "head_linear: gate mode %d", gate_mode);
   TGE_REQUIRE(heads <= 65535 && (n_out + HL_BN - 1) / HL_BN <= 65535, "head_linear: too many heads or outputs for one launch");
   if (tokens == 0) return 0;
+  if (tokens <= HL_ROWS_MAX_TOKENS) {
+    dim3 small(heads, (n_out + 7) / 8);
+    if (is_bf16)
+      tge_launch(head_linear_rows_kernel<__nv_bfloat16>, small, dim3(256), 0, stream, (const __nv_bfloat16*)x, x_row, x_head,
+                 (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_row, out_head, gate, gate_mode, gate_row, tokens, n_out, k_in);
+    else
+      tge_launch(head_linear_rows_kernel<float>, small, dim3(256), 0, stream, (const float*)x, x_row, x_head, (const float*)w,
+                 (float*)out, out_row, out_head, gate, gate_mode, gate_row, tokens, n_out, k_in);
+    return tge_launched("head_linear", 1);
+  }
   dim3 grid((tokens + HL_BM - 1) / HL_BM, heads, (n_out + HL_BN - 1) / HL_BN);
   if (is_bf16)
     tge_launch(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)x, x_row, x_head,

@@ -40,6 +40,14 @@ from .base import (MIXERS, POSITIONS, LayerCache, Mixer, PagedCacheSpec, ParamSp
 
 
 _EXPANDED: Dict[tuple, tuple] = {}      # the steps' own key and value pages, per device and geometry
+_SMS: Dict[int, int] = {}
+
+
+def _sm_count(device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _SMS:
+        _SMS[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _SMS[index]
 
 
 @MIXERS.register("latent_attention")
@@ -161,10 +169,26 @@ class LatentAttention(Mixer):
         if self.rot:
             ops.rotate_interleaved(q[:, self.dim:], per_head, queries[:, self.kv_rank:], self.entry, self.heads, self.rot,
                                    self.cos, self.sin, self.rot_dims, ctx.positions)
-        attended = ops.attention(queries, pages, None, table, ctx.q_start, ctx.start_pos, ctx.positions, ctx.seq_of_token,
-                                 ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads, 1, self.entry, self.scale,
-                                 split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
-                                 decode_prefix=ctx.decode_prefix, values_in_keys=self.kv_rank)
+        # single tokens: the decode kernels take the heads that share a key/value head as the rows of one tile of 16,
+        # so more heads than that go in equal runs of up to 16 (the entries are few bytes; reading them twice is cheap)
+        single = ctx.max_q_len <= 1 and dtype == torch.bfloat16
+        runs = -(-self.heads // 16) if single else 1
+        size = -(-self.heads // runs)
+        split = ctx.attn_split_tokens
+        if single and split == 0 and self.entry > 128:
+            # entries this wide leave room for one block of the decode kernel per SM, so the keys are cut into just
+            # enough runs to give every SM a block, not into the many short ones that suit narrow heads
+            bound = max(ctx.typical_ctx_len or ctx.max_ctx_len, 1)
+            want = max(_sm_count(h.device) // max(ctx.num_seqs, 1), 1)
+            split = max(64 * -(-(-(-bound // want)) // 64), 128)
+        attended = torch.empty((tokens, self.heads * self.kv_rank), dtype=dtype, device=h.device)
+        for lo in range(0, self.heads, size):
+            n = min(size, self.heads - lo)
+            ops.attention(queries[:, lo * self.entry:(lo + n) * self.entry], pages, None, table, ctx.q_start, ctx.start_pos,
+                          ctx.positions, ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, n, 1, self.entry,
+                          self.scale, split_tokens=split, typical_ctx_len=ctx.typical_ctx_len,
+                          decode_prefix=ctx.decode_prefix, values_in_keys=self.kv_rank,
+                          out=attended[:, lo * self.kv_rank:(lo + n) * self.kv_rank])
         if out is None:
             out = torch.empty((tokens, self.heads * self.vdim), dtype=dtype, device=h.device)
         mode = {"none": 0, "head": 1, "element": 2}[self.gate]
