@@ -231,14 +231,14 @@ def puputar_config(width: int, heads: int, head_dim: int, gated_inner: int, laye
     """A Puputar config.json with the width, heads, head size and layer count of a Qwen2 shape: queries and keys of
     ``head_dim`` numbers (half of them rotated), values of ``head_dim``, a query latent of a quarter of the width, cache
     entries of 192 + head_dim / 2 numbers; layers by turns with the dense feed-forward (two matrices of one and a
-    half times the gated inner width) and with ``experts`` small experts and two identity experts of which ``top`` are
-    used (together as wide as the dense one); every fourth layer reads the entries of the routed layer before it."""
+    half times the gated inner width) and with ``experts`` small experts and four identity experts, in four groups of
+    which two are kept, of which ``top`` are used (together as wide as the dense one); every fourth layer reads the entries of the routed layer before it."""
     rot = head_dim // 2
     mixer = {"heads": heads, "dim": head_dim - rot, "rot_dim": rot, "vdim": head_dim, "q_rank": max(width // 4 // 64 * 64, 64),
              "kv_rank": 192, "scale": head_dim ** -0.5, "rot": {"base": 500000.0, "dims": rot}}
     dense = {"kind": "dense", "ff": gated_inner * 3 // 2}
     routed = {"kind": "moe", "expert": {"ff": max(gated_inner * 3 // 2 // top // 64 * 64, 64)},
-              "router": {"experts": experts, "top": top, "identity": 2, "groups": {"count": 2, "keep": 1}}}
+              "router": {"experts": experts, "top": top, "identity": 4, "groups": {"count": 4, "keep": 2}}}
     out = []
     for n in range(layers):
         if n % 2 == 0:
