@@ -15,11 +15,12 @@ portion), the same figures with the engine's default pages of 64 tokens, long
 contexts, and the 14B and 32B shapes.  This engine runs on one GPU: for --gpus
 above 1 it says so and exits with 2.
 
-    python bench.py --compare lepizen|mozepel|puputar [--compare-sizes 7b,14b,1.5b] [--steps K]
+    python bench.py --compare lepizen|mozepel|puputar [--compare-sizes 7b,14b,1.5b] [--steps K] [--compare-timelines first|all|none]
 
-is another measurement and leaves the one above alone: the Lepizen or the Mozepel design beside the Qwen2 design at equal
-width, heads, layers and vocabulary (Lepizen: and parameter count), at sizes of real models' layers (random weights), prefill
-and decode, with the kernels of one step of each.  It prints one JSON line {"compare": ...}.
+is another measurement and leaves the one above alone: the Lepizen, Mozepel or Puputar design beside the Qwen2 design at
+equal width, heads, layers and vocabulary (Lepizen: and parameter count), at sizes of real models' layers (random weights),
+prefill and decode, with the kernels of one step of each at the first size (or all sizes).  It prints one JSON line
+{"compare": ...}.
 """
 import argparse
 import json
@@ -171,7 +172,9 @@ def compare(args) -> int:
         width, heads, kv_heads, head_dim, inner = COMPARE_SIZES[size]
         configs = paired_configs(width, heads, kv_heads, head_dim, inner, args.compare_layers, CONFIG_7B["vocab_size"])
         configs = {name: configs[name] for name in ("qwen2", args.compare)}
-        out["sizes"][size] = compare_designs(configs, prompt_len=PROMPT, steps=min(args.steps, 32), warmup=max(args.warmup, 3))
+        timelines = args.compare_timelines == "all" or (args.compare_timelines == "first" and size == sizes[0])
+        out["sizes"][size] = compare_designs(configs, prompt_len=PROMPT, steps=min(args.steps, 32), warmup=max(args.warmup, 3),
+                                             timelines=timelines)
     ops.check_status()
     print(json.dumps({"compare": out}))
     return 0
@@ -189,6 +192,8 @@ def main() -> int:
     parser.add_argument("--compare", choices=["lepizen", "mozepel", "puputar"], help="instead of the headline: this design beside Qwen2 at equal size")
     parser.add_argument("--compare-sizes", default="7b,14b,1.5b", help="which of 1.5b, 7b, 14b (layer shapes), with commas")
     parser.add_argument("--compare-layers", type=int, default=8, help="layers of each model in --compare")
+    parser.add_argument("--compare-timelines", choices=["first", "all", "none"], default="first",
+                        help="kernel timelines (under the torch profiler) in --compare: of the first size, of all, of none")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
