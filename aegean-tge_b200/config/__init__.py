@@ -9,7 +9,9 @@ from .mozepel import ARCHITECTURE as MOZEPEL_ARCHITECTURE
 from .mozepel import MozepelConfig
 from .puputar import ARCHITECTURE as PUPUTAR_ARCHITECTURE
 from .puputar import PuputarConfig
+from .kokolorn import ARCHITECTURE as KOKOLORN_ARCHITECTURE
+from .kokolorn import KokolornConfig
 
-__all__ = ["PuputarConfig", "PUPUTAR_ARCHITECTURE", "LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
+__all__ = ["KokolornConfig", "KOKOLORN_ARCHITECTURE", "PuputarConfig", "PUPUTAR_ARCHITECTURE", "LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
            "Qwen2Config", "QWEN2_ARCHITECTURE", "LepizenConfig", "LEPIZEN_ARCHITECTURE", "MozepelConfig", "MOZEPEL_ARCHITECTURE",
            "read_config_json"]

@@ -38,7 +38,10 @@ class LayerSpec:
     ``block_params`` are the arrangement's own constants (a residual multiplier).
     ``weights_from`` names an earlier layer whose parts this layer runs (the same
     tensors, loaded once), with a cache and state of its own; its part specs
-    then equal that layer's.
+    then equal that layer's.  ``entry`` is a stream step that runs right before
+    the layer on every visit (the stream mixed with the embedding output again
+    at the head of a pass over a run of layers); it belongs to the visit, not to
+    the borrowed parts.
     """
 
     block: str
@@ -49,6 +52,7 @@ class LayerSpec:
     cache_from: Optional[int] = None
     block_params: Mapping[str, Any] = field(default_factory=dict)
     weights_from: Optional[int] = None
+    entry: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -117,6 +121,9 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, str]:
     add(spec.final_norm, "final_norm")
     add(spec.head, "head")
     for index, layer in enumerate(spec.layers):
+        add(layer.entry, f"layers[{index}].entry")
+        if layer.weights_from is not None:
+            continue
         add(layer.mixer_norm, f"layers[{index}].mixer_norm")
         add(layer.mixer, f"layers[{index}].mixer")
         add(layer.ffn_norm, f"layers[{index}].ffn_norm")

@@ -15,6 +15,8 @@
 // With a window and `pool` > 0 the query also sees, in the same softmax, one pooled key and value for every
 // block of `pool` positions that lies wholly before its window (block b if b*pool + pool - 1 <= p - window); they
 // are read from pages of their own, entry b where position b would be, and visited before the tokens.
+// `dist_bias` [heads, span] (float32): a learned bias added to the scaled score of the key at distance n, entry
+// min(n, span - 1) of the head's row.
 #include "common.cuh"
 
 namespace {
@@ -28,12 +30,14 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, T* __restrict__ out, int out_stride,
     int heads, int kv_heads, int head_dim, int value_dim, int v_pitch, const float* __restrict__ sink, float scale, int window,
     int pool, const T* __restrict__ kp_pages, const T* __restrict__ vp_pages, const int* __restrict__ pool_table,
-    int pool_max_pages, int pool_num_pages, int* status) {
+    int pool_max_pages, int pool_num_pages, const float* __restrict__ dist_bias, int dist_span, int* status) {
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * 4 + warp;
   if (h >= heads) return;
   const int group = heads / kv_heads;
+  // a learned bias by distance, unscaled: row h of [heads, span], distances from span - 1 on share the last entry
+  const float* bias_row = dist_bias != nullptr ? dist_bias + (size_t)h * dist_span : nullptr;
   const int kvh = h / group;
   const int pos = positions[t];
   const int seq = seq_of_token[t];
@@ -101,7 +105,8 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
         if (d < head_dim) dot = fmaf(qv[i], to_float<T>(krow[d]), dot);
       }
       dot = warp_sum(dot);
-      const float s = dot * scale;
+      float s = dot * scale;
+      if (bias_row != nullptr) s += bias_row[min(pos - (page_index * page_size + slot), dist_span - 1)];
       const float m_new = fmaxf(m, s);
       const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
       const float p = expf(s - m_new);
@@ -226,8 +231,8 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
                                const int* positions, const int* seq_of_token, void* out, int out_stride, int tokens,
                                int heads, int kv_heads, int head_dim, int value_dim, const float* sink, float scale,
                                int window, int is_bf16, int pool, const void* kp_pages, const void* vp_pages,
-                               const int* pool_table, int pool_max_pages, int pool_num_pages, int v_pitch, int* status,
-                               cudaStream_t stream) {
+                               const int* pool_table, int pool_max_pages, int pool_num_pages, int v_pitch,
+                               const float* dist_bias, int dist_span, int* status, cudaStream_t stream) {
   // v_pitch: numbers between the starts of two positions' values in `v_pages` (0: value_dim, values packed).  A cache
   // whose values are the leading part of its keys passes the keys' pages twice and the keys' size here.
   if (v_pitch == 0) v_pitch = value_dim;
@@ -241,6 +246,7 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
               32 * MAX_PER_LANE);
   TGE_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad page geometry");
   TGE_REQUIRE(window >= 0, "attention: negative window");
+  TGE_REQUIRE(dist_bias == nullptr || dist_span > 0, "attention: a bias by distance needs its span");
   TGE_REQUIRE(pool >= 0 && (pool == 0 || (window > 0 && kp_pages != nullptr && vp_pages != nullptr && pool_table != nullptr &&
                                           pool_max_pages > 0 && pool_num_pages > 0)),
               "attention: pooled blocks need a window, their pages and their table");
@@ -251,12 +257,13 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
         max_pages, num_pages, page_size, positions, seq_of_token, (__nv_bfloat16*)out, out_stride, heads, kv_heads,
         head_dim, value_dim, v_pitch, sink, scale, window, pool, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages,
-        pool_table, pool_max_pages, pool_num_pages, status);
+        pool_table, pool_max_pages, pool_num_pages, dist_bias, dist_span, status);
   else
     attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
         (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_pages, num_pages,
         page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, v_pitch, sink, scale,
-        window, pool, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, status);
+        window, pool, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, dist_bias,
+        dist_span, status);
   return tge_launched("attention_simt", 1);
 }
 

@@ -8,11 +8,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// embedding: x[t, :] = table[ids[t], :] as float32
+// embedding: x[t, :] = table[ids[t], :] * scale as float32
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -24,18 +24,18 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float<T>(src[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float<T>(src[i]) * scale;
 }
 
 TGE_API int tge_embedding(const void* table, int is_bf16, const int* ids, float* out, int tokens,
-                          int hidden, int vocab, int* status, cudaStream_t stream) {
+                          int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes tokens=%d hidden=%d vocab=%d",
               tokens, hidden, vocab);
   if (tokens == 0) return 0;
   if (is_bf16)
-    tge_launch(embedding_kernel<__nv_bfloat16>, tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+    tge_launch(embedding_kernel<__nv_bfloat16>, tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, status);
   else
-    tge_launch(embedding_kernel<float>, tokens, 256, 0, stream, (const float*)table, ids, out, hidden, vocab, status);
+    tge_launch(embedding_kernel<float>, tokens, 256, 0, stream, (const float*)table, ids, out, hidden, vocab, scale, status);
   return tge_launched("embedding", 1);
 }
 

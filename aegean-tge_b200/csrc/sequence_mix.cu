@@ -678,11 +678,12 @@ __global__ void decay_segment_carry_kernel(float* __restrict__ carry, float* __r
 }
 
 // out[t, g*size + e] = o[t, g*size + e] / rms_g(o[t]) * weight[g*size + e] * act(gate[t, g*size + e]); one warp per
-// (token, group).  weight may be null (no weight); act 0: silu, 1: sigmoid.
-template <typename T>
+// (token, group).  weight may be null (no weight); act 0: silu, 1: sigmoid; act 2: the SiLU gate comes BEFORE the norm,
+// out = y / rms_g(y) * weight with y = o * silu(gate).
+template <typename T, typename TO = T>
 __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate,
                                                          long long ld_gate, const float* __restrict__ weight,
-                                                         T* __restrict__ out, long long ld_out, int tokens, int groups,
+                                                         TO* __restrict__ out, long long ld_out, int tokens, int groups,
                                                          int size, float eps, int act) {
   pdl_trigger();
   pdl_wait();
@@ -691,16 +692,28 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict
   if (unit >= (long long)tokens * groups) return;
   const int t = (int)(unit / groups), g = (int)(unit - (long long)t * groups);
   const float* src = o + ((size_t)t * groups + g) * size;
+  const T* gt = gate + (size_t)t * ld_gate + (size_t)g * size;
+  TO* dst = out + (size_t)t * ld_out + (size_t)g * size;
   float sum = 0.0f;
+  if (act == 2) {
+    for (int e = lane; e < size; e += 32) {
+      const float y = src[e] * silu_f(to_float<T>(gt[e]));
+      sum = fmaf(y, y, sum);
+    }
+    const float scale = 1.0f / sqrtf(warp_sum(sum) / (float)size + eps);
+    for (int e = lane; e < size; e += 32) {
+      const float w = weight != nullptr ? weight[(size_t)g * size + e] : 1.0f;
+      dst[e] = from_float<TO>(src[e] * silu_f(to_float<T>(gt[e])) * scale * w);
+    }
+    return;
+  }
   for (int e = lane; e < size; e += 32) sum = fmaf(src[e], src[e], sum);
   sum = warp_sum(sum);
   const float scale = 1.0f / sqrtf(sum / (float)size + eps);
-  const T* gt = gate + (size_t)t * ld_gate + (size_t)g * size;
-  T* dst = out + (size_t)t * ld_out + (size_t)g * size;
   for (int e = lane; e < size; e += 32) {
     const float z = to_float<T>(gt[e]);
     const float w = weight != nullptr ? weight[(size_t)g * size + e] : 1.0f;
-    dst[e] = from_float<T>(src[e] * scale * w * (act == 0 ? silu_f(z) : sigmoid_f(z)));
+    dst[e] = from_float<TO>(src[e] * scale * w * (act == 0 ? silu_f(z) : sigmoid_f(z)));
   }
 }
 
@@ -1029,13 +1042,19 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
 }
 
 TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long long ld_gate, const float* weight, void* out,
-                           long long ld_out, int tokens, int groups, int size, float eps, int act, cudaStream_t stream) {
+                           long long ld_out, int tokens, int groups, int size, float eps, int act, int out_is_bf16,
+                           cudaStream_t stream) {
+  // the gate may arrive in float32 (a product that stored it so) while the rows go on in bfloat16
+  TGE_REQUIRE(out_is_bf16 == is_bf16 || (!is_bf16 && out_is_bf16), "gated_norm: a bfloat16 gate goes with bfloat16 rows");
   TGE_REQUIRE(tokens >= 0 && groups > 0 && size > 0, "gated_norm: bad shape");
-  TGE_REQUIRE(act == 0 || act == 1, "gated_norm: the gate is silu (0) or sigmoid (1)");
+  TGE_REQUIRE(act >= 0 && act <= 2, "gated_norm: the gate is silu (0), sigmoid (1) or silu before the norm (2)");
   if (tokens == 0) return 0;
   const long long units = (long long)tokens * groups;
   const unsigned blocks = (unsigned)((units + 3) / 4);
-  if (is_bf16)
+  if (!is_bf16 && out_is_bf16)
+    tge_launch(gated_norm_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, (const float*)gate, ld_gate, weight,
+               (__nv_bfloat16*)out, ld_out, tokens, groups, size, eps, act);
+  else if (is_bf16)
     tge_launch(gated_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, ld_gate,
                weight, (__nv_bfloat16*)out, ld_out, tokens, groups, size, eps, act);
   else

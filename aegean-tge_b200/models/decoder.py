@@ -16,8 +16,8 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..config.model_spec import ModelSpec, PartSpec
-from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, BuildEnv, LayerCache,
-                          ParamSpec, Part, StepContext, build_part)
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_STEPS, Block, BuildEnv,
+                          LayerCache, ParamSpec, Part, StepContext, build_part)
 
 
 class DecoderModel:
@@ -29,6 +29,9 @@ class DecoderModel:
         self.final_norm = build_part(NORMS, spec.final_norm, env)
         self.head = build_part(HEADS, spec.head, env)
         self.blocks: List[Block] = []
+        # what runs right before a layer on each visit (None for most): a visit's own, also where the parts are borrowed
+        self.entries: List[Optional[Part]] = [build_part(STREAM_STEPS, layer.entry, env) if layer.entry is not None else None
+                                              for layer in spec.layers]
         for layer in spec.layers:
             if layer.weights_from is not None:
                 # the same parts once more: parts hold weights only, what a layer keeps lives in its LayerCache
@@ -53,6 +56,8 @@ class DecoderModel:
                                                  ("final_norm", self.final_norm, self.spec.final_norm),
                                                  ("head", self.head, self.spec.head)]
         for index, (block, layer) in enumerate(zip(self.blocks, self.spec.layers)):
+            if self.entries[index] is not None:
+                out.append((f"layers[{index}].entry", self.entries[index], layer.entry))
             if layer.weights_from is not None:
                 continue
             out.append((f"layers[{index}].mixer_norm", block.mixer_norm, layer.mixer_norm))
@@ -98,6 +103,8 @@ class DecoderModel:
         with the tokens says so through ``step_param_bytes``), the embedding rows not counted."""
         total = self.final_norm.param_bytes() + self.head.param_bytes()
         for index in self.spec.schedule:
+            if self.entries[index] is not None:
+                total += self.entries[index].param_bytes()
             for part in self.blocks[index].parts().values():
                 grows = getattr(part, "step_param_bytes", None)
                 total += grows(tokens) if grows is not None else part.param_bytes()
@@ -141,7 +148,7 @@ class DecoderModel:
         for param, _where in self.manifest().values():
             count = 1
             for extent in param.shape:
-                count *= int(extent)
+                count *= max(int(extent), 0)
             total += count * (self.env.dtype.itemsize if param.role == "matrix" else 4)
         return total
 
@@ -150,6 +157,8 @@ class DecoderModel:
         meeting ``pairs`` (query, key) pairs per layer, and ``rows`` rows of logits."""
         total = self.head.flops(rows, 0.0)
         for index in self.spec.schedule:
+            if self.entries[index] is not None:
+                total += self.entries[index].flops(tokens, pairs)
             total += sum(part.flops(tokens, pairs) for part in self.blocks[index].parts().values())
         return total
 
@@ -158,11 +167,17 @@ class DecoderModel:
         """Runs the step's tokens through all layers; returns float32 logits [R, vocab] of the wanted rows."""
         x = self.embedding.forward(ctx.token_ids)
         schedule = self.spec.schedule
+        # a stream step reads the embedding output: kept aside only if some layer has one
+        x0 = x.clone() if any(self.entries[index] is not None for index in schedule) else None
         h = None                              # the next layer's first norm, when the previous layer produced it
         for step, index in enumerate(schedule):
             after = self.blocks[schedule[step + 1]] if step + 1 < len(schedule) else None
+            if after is not None and self.entries[schedule[step + 1]] is not None:
+                after = None                  # the stream changes before the next layer: nothing of it can be normed ahead
             following = after.mixer_norm if after is not None else None
             block = self.blocks[index]
+            if self.entries[index] is not None:
+                self.entries[index].forward(x, x0, ctx)
             more = ({"next_takes_deferred": after is not None and after.mixer.takes_deferred_rows}
                     if block.passes_deferred_rows else {})
             h = block.forward(x, ctx, self.layer_caches[index], h=h, next_norm=following, **more)

@@ -56,7 +56,7 @@ def core() -> ctypes.CDLL:
         path = _build.build_core()
         lib = ctypes.CDLL(path)
         lib.tge_last_error.restype = ctypes.c_char_p
-        _declare(lib, "tge_embedding", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_embedding", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr])
         _declare(lib, "tge_rmsnorm", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float,
                                       _c_ptr, _c_ptr])
         _declare(lib, "tge_add_to_stream", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_float, _c_ptr])
@@ -93,7 +93,7 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
-                                             _c_int, _c_ptr, _c_ptr])
+                                             _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_attention_pooled_merge", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                                      _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
@@ -132,7 +132,7 @@ def core() -> ctypes.CDLL:
                                          _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                          _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr])
         _declare(lib, "tge_gated_norm", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
-                                         _c_float, _c_int, _c_ptr])
+                                         _c_float, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_conv_norm_rope_store", [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                                    _c_ptr, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
                                                    _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int,
@@ -151,6 +151,18 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_random_fill", [_c_ptr, _c_int, _c_ll, _c_ll, ctypes.c_ulonglong, _c_int, _c_float, _c_int,
                                           ctypes.c_uint, _c_ptr])
         _declare(lib, "tge_wait_gives_up", [_c_ptr, _c_ll, _c_ptr, _c_ptr])
+        _declare(lib, "tge_gated_prepare", [_c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_float, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_gated_rule_scan", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                              _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_norm_scale_add", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_float, _c_float, _c_ptr])
+        _declare(lib, "tge_qk_temp_store", [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_float, _c_int, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_gated_clamp_act", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_float,
+                                              _c_float, _c_ptr])
+        _declare(lib, "tge_concat_rows", [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr])
         lib.tge_device_sm_count.argtypes = []
         lib.tge_device_sm_count.restype = _c_int
         lib.tge_sample_cuts_padded.argtypes = [_c_int]
@@ -298,8 +310,8 @@ def scratch_floats(count: int) -> torch.Tensor:
 # ----------------------------------------------------------------------------
 # kernels
 # ----------------------------------------------------------------------------
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, :] = float32(table[ids[t], :])"""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]) * scale"""
     _want(table, "embedding table", _FLOAT)
     _want(ids, "token ids", torch.int32)
     vocab, hidden = table.shape
@@ -309,7 +321,7 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor
     _want(out, "embedding output", torch.float32)
     lib = core()
     _check(lib.tge_embedding(table.data_ptr(), int(table.dtype == torch.bfloat16), ids.data_ptr(), out.data_ptr(),
-                             tokens, hidden, vocab, status_word().data_ptr(), _stream()), lib)
+                             tokens, hidden, vocab, float(scale), status_word().data_ptr(), _stream()), lib)
     return out
 
 
@@ -738,7 +750,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0,
               sink: Optional[torch.Tensor] = None, pool: int = 0, pooled_k: Optional[torch.Tensor] = None,
               pooled_v: Optional[torch.Tensor] = None, pool_table: Optional[torch.Tensor] = None,
-              values_in_keys: int = 0) -> torch.Tensor:
+              values_in_keys: int = 0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
@@ -756,6 +768,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     through ``pool_table``.  Served by the CUDA-core kernel.
     ``values_in_keys`` > 0: a position's value is the first that many numbers of its key entry (a latent cache whose
     entries serve as keys whole and as values in part); ``v_pages`` is then not used and may be None.
+    ``dist_bias`` (float32 [heads, span]): a learned bias by distance, added unscaled to the scaled score of the key
+    that lies n positions back, entry min(n, span - 1) of the head's row.  Served by the CUDA-core kernel.
     """
     v_pitch = 0
     if values_in_keys:
@@ -800,7 +814,14 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
             raise KernelError(f"pooled pages must be shaped like the keys' and values', got {tuple(pooled_k.shape)} "
                               f"and {tuple(pooled_v.shape)}")
         pool_pages, pool_width = pooled_k.shape[0], pool_table.shape[1]
-    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
+    dist_span = 0
+    if dist_bias is not None:
+        _want(dist_bias, "bias by distance", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != heads or pool:
+            raise KernelError(f"attention: a bias by distance is [heads, span] (and goes without pooled blocks), got "
+                              f"{tuple(dist_bias.shape)}")
+        dist_span = dist_bias.shape[1]
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok and dist_bias is None
                and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim)
                and not (v_pitch and value_dim == head_dim))
     if use_mma:
@@ -853,7 +874,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                   seq_of_token.data_ptr(), out.data_ptr(), out_stride, tokens, heads, kv_heads,
                                   head_dim, value_dim, _ptr(sink), float(scale), window, int(q.dtype == torch.bfloat16),
                                   int(pool), _ptr(pooled_k), _ptr(pooled_v), _ptr(pool_table), pool_width, pool_pages,
-                                  v_pitch, status_word().data_ptr(), _stream()), lib)
+                                  v_pitch, _ptr(dist_bias), dist_span, status_word().data_ptr(), _stream()), lib)
     return out
 
 
@@ -937,10 +958,12 @@ def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: in
 
 
 def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], groups: int, eps: float,
-               sigmoid: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               sigmoid: bool, out: Optional[torch.Tensor] = None, gate_first: bool = False,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out = o / rms(o) * weight * act(gate), the root mean square taken over each of ``groups`` equal runs of a
     row (one per head, or 1: all heads together).  ``o`` float32 [T, n]; ``gate`` run dtype [T, n] (dense rows, any
-    row stride); ``weight`` float32 [n] or None; act is SiLU, or the logistic function with ``sigmoid``."""
+    row stride; it may be float32 while the rows go on in bfloat16: ``out_dtype``); ``weight`` float32 [n] or None; act is SiLU, or the logistic function with ``sigmoid``.  With
+    ``gate_first`` the SiLU gate comes before the norm: out = y / rms(y) * weight, y = o * silu(gate)."""
     _want(o, "readout", torch.float32)
     _want(gate, "gate", _FLOAT, contiguous=False)
     tokens, width = o.shape
@@ -951,12 +974,13 @@ def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tenso
         if weight.numel() != width:
             raise KernelError(f"gated_norm: weight has {weight.numel()} elements for rows of {width}")
     if out is None:
-        out = torch.empty((tokens, width), dtype=gate.dtype, device=o.device)
-    _want(out, "gated_norm output", gate.dtype, contiguous=False)
+        out = torch.empty((tokens, width), dtype=out_dtype or gate.dtype, device=o.device)
+    _want(out, "gated_norm output", _FLOAT, contiguous=False)       # a float32 gate may go with bfloat16 rows
     lib = core()
     _check(lib.tge_gated_norm(o.data_ptr(), gate.data_ptr(), int(gate.dtype == torch.bfloat16), _rows_2d(gate, "gate"),
                               _ptr(weight), out.data_ptr(), _rows_2d(out, "gated_norm output"), tokens, groups,
-                              width // groups, float(eps), int(sigmoid), _stream()), lib)
+                              width // groups, float(eps), 2 if gate_first else int(sigmoid),
+                              int(out.dtype == torch.bfloat16), _stream()), lib)
     return out
 
 
@@ -1501,3 +1525,164 @@ def experts_combine_add(outputs: torch.Tensor, place: torch.Tensor, weights: tor
     _check(lib.tge_experts_combine_add(outputs.data_ptr(), place.data_ptr(), weights.data_ptr(), h.data_ptr(),
                                        _rows_2d(h, "expert input"), x.data_ptr(), tokens, top, width,
                                        int(h.dtype == torch.bfloat16), _stream()), lib)
+
+
+# ----------------------------------------------------------------------------
+# mixers with a matrix state that every token decays, corrects and reads; what surrounds them
+# ----------------------------------------------------------------------------
+GATED_DELTA, GATED_STATE_SPACE = 0, 1
+
+
+def gated_prepare(raw: torch.Tensor, mode: int, groups: int, heads: int, dim: int, vdim: int, taps: int,
+                  conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], tails: Optional[torch.Tensor], slots: torch.Tensor,
+                  q_start: torch.Tensor, seq_of_token: torch.Tensor, num_seqs: int, a_log: torch.Tensor,
+                  dt_bias: torch.Tensor, unit_eps: float = 1e-6, q_scale: float = 1.0):
+    """What the recurrence of :func:`gated_rule_scan` takes, from a mixer's input product ``raw`` (float32 [T, n]).
+
+    ``GATED_DELTA``: raw = [q | k | v | gate | b | a] with q and k of ``groups`` heads x dim and v of heads x vdim;
+    q, k and v pass a causal convolution over time per channel (``conv_w`` float32 [channels, taps], the last tap the
+    current token's; ``tails`` float32 [slots, taps-1, channels] holds every request's last inputs and is brought up
+    to date) and SiLU; q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times ``q_scale``;
+    decay = exp(-exp(a_log) softplus(a + dt_bias)), strength = sigmoid(b).
+    ``GATED_STATE_SPACE``: raw = [z | x | B | C | dt] with x of heads x vdim and B, C of ``groups`` x dim; x, B and C
+    pass the convolution (with ``conv_b``) and SiLU; q = C, k = B; dt <- softplus(dt + dt_bias), decay =
+    exp(-exp(a_log) dt), strength = dt.
+    Returns (qk float32 [T, groups, 2, dim], v float32 [T, heads * vdim], gates float32 [T, heads, 2])."""
+    _want(raw, "projections", torch.float32, contiguous=False)
+    ld = _rows_2d(raw, "projections")
+    tokens = raw.shape[0]
+    channels = 2 * groups * dim + heads * vdim
+    _want(conv_w, "convolution taps", torch.float32)
+    if tuple(conv_w.shape) != (channels, taps):
+        raise KernelError(f"gated_prepare: taps must be [{channels}, {taps}], got {tuple(conv_w.shape)}")
+    if conv_b is not None:
+        _want(conv_b, "convolution bias", torch.float32)
+        if conv_b.numel() != channels:
+            raise KernelError(f"gated_prepare: the convolution's bias has {conv_b.numel()} elements for {channels} channels")
+    if taps > 1:
+        _want(tails, "convolution tails", torch.float32)
+        if tails.dim() != 3 or tuple(tails.shape[1:]) != (taps - 1, channels):
+            raise KernelError(f"gated_prepare: tails must be [slots, {taps - 1}, {channels}], got {tuple(tails.shape)}")
+    for name, t in (("slots", slots), ("q_start", q_start), ("seq_of_token", seq_of_token)):
+        _want(t, name, torch.int32)
+    for name, t in (("a_log", a_log), ("dt_bias", dt_bias)):
+        _want(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"gated_prepare: {name} has {t.numel()} elements for {heads} heads")
+    qk = torch.empty((tokens, groups, 2, dim), dtype=torch.float32, device=raw.device)
+    v = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=raw.device)
+    gates = torch.empty((tokens, heads, 2), dtype=torch.float32, device=raw.device)
+    lib = core()
+    _check(lib.tge_gated_prepare(raw.data_ptr(), ld, int(mode), groups, heads, dim, vdim, taps, conv_w.data_ptr(),
+                                 _ptr(conv_b), _ptr(tails) if taps > 1 else None, slots.data_ptr(), q_start.data_ptr(),
+                                 seq_of_token.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), float(unit_eps),
+                                 float(q_scale), qk.data_ptr(), v.data_ptr(), gates.data_ptr(), tokens, num_seqs,
+                                 _stream()), lib)
+    return qk, v, gates
+
+
+def gated_rule_scan(qk: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+                    q_start: torch.Tensor, num_seqs: int, delta: bool, skip: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per head and request, token by token in float32: S <- a S; u = b (v - S^T k) with ``delta``, else u = b v;
+    S <- S + k u^T; o = S^T q + skip v.  ``qk`` [T, groups, 2, dim] (q then k), ``v`` [T, heads * vdim], ``gates``
+    [T, heads, 2] = (a, b), ``state`` float32 [slots, heads, dim, vdim] read and written in row ``slots[s]``; head h
+    uses group h // (heads / groups); ``skip`` float32 [heads] or None.  Returns o float32 [T, heads * vdim]."""
+    for name, t in (("q and k", qk), ("values", v), ("gates", gates), ("state", state)):
+        _want(t, name, torch.float32)
+    tokens, groups, _two, dim = qk.shape
+    heads = gates.shape[1]
+    vdim = v.shape[1] // heads
+    if (tuple(v.shape) != (tokens, heads * vdim) or tuple(gates.shape) != (tokens, heads, 2) or state.dim() != 4
+            or tuple(state.shape[1:]) != (heads, dim, vdim) or heads % groups):
+        raise KernelError(f"gated_rule_scan: q/k {tuple(qk.shape)}, values {tuple(v.shape)}, gates {tuple(gates.shape)}, "
+                          f"state {tuple(state.shape)}")
+    if skip is not None:
+        _want(skip, "skip weights", torch.float32)
+        if skip.numel() != heads:
+            raise KernelError(f"gated_rule_scan: {skip.numel()} skip weights for {heads} heads")
+    _want(slots, "slots", torch.int32)
+    _want(q_start, "q_start", torch.int32)
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=qk.device)
+    lib = core()
+    _check(lib.tge_gated_rule_scan(qk.data_ptr(), v.data_ptr(), gates.data_ptr(), _ptr(skip), int(delta), heads, groups, dim,
+                                   vdim, state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), num_seqs,
+                                   tokens, _stream()), lib)
+    return out
+
+
+def norm_scale_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, alpha: float = 1.0) -> None:
+    """x (float32 [T, H]) += alpha * y / sqrt(mean(y^2) + eps) * weight, row by row; y float32 (dense rows)."""
+    _want(x, "stream", torch.float32)
+    _want(y, "addend", torch.float32, contiguous=False)
+    _want(weight, "norm weight", torch.float32)
+    if x.shape != y.shape or weight.numel() != x.shape[1]:
+        raise KernelError(f"norm_scale_add: {tuple(x.shape)}, {tuple(y.shape)}, weight of {weight.numel()}")
+    lib = core()
+    _check(lib.tge_norm_scale_add(x.data_ptr(), y.data_ptr(), _rows_2d(y, "addend"), weight.data_ptr(), x.shape[0],
+                                  x.shape[1], float(alpha), float(eps), _stream()), lib)
+
+
+def qk_temp_store(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                  temp_coef: float, temp_every: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                  block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                  heads: int, kv_heads: int, head_dim: int) -> None:
+    """After the q/k product of an attention whose values are its keys as projected: rows ``qk`` [T, q | k].  The
+    values' pages get k as it arrives; q and k are then normalised per head (weights float32 [head_dim], None: not
+    normalised), q is multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (``temp_every`` 0: not) and
+    rewritten in place, and k goes to its pages.  Pages None: nothing is stored."""
+    _want(qk, "q and k", _FLOAT, contiguous=False)
+    stride = _rows_2d(qk, "q and k")
+    for name, t in (("q norm weight", q_weight), ("k norm weight", k_weight)):
+        if t is not None:
+            _want(t, name, torch.float32)
+            if t.numel() != head_dim:
+                raise KernelError(f"{name} has {t.numel()} elements for heads of {head_dim}")
+    _want(positions, "positions", torch.int32)
+    _want(seq_of_token, "seq_of_token", torch.int32)
+    store = k_pages is not None
+    num_pages = page_size = max_pages = 0
+    if store:
+        _want(k_pages, "k pages", qk.dtype)
+        _want(v_pages, "v pages", qk.dtype)
+        _want(block_table, "block table", torch.int32)
+        num_pages, _, page_size, _ = k_pages.shape
+        if tuple(k_pages.shape) != (num_pages, kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape:
+            raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pages.shape)} and "
+                              f"{tuple(v_pages.shape)}")
+        max_pages = block_table.shape[1]
+    lib = core()
+    _check(lib.tge_qk_temp_store(qk.data_ptr(), int(qk.dtype == torch.bfloat16), stride, _ptr(q_weight), _ptr(k_weight),
+                                 float(eps), float(temp_coef), int(temp_every), positions.data_ptr(), seq_of_token.data_ptr(),
+                                 _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages), num_pages, page_size,
+                                 qk.shape[0], heads, kv_heads, head_dim, int(store), status_word().data_ptr(), _stream()), lib)
+
+
+def gated_clamp_act(rows: torch.Tensor, limit: float, alpha: float, offset: float, out_dtype: torch.dtype,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``rows`` float32 [T, 2 n] with (g_i, u_i) side by side -> [T, n]: min(g, L) sigmoid(alpha min(g, L))
+    (clamp(u, -L, L) + offset)."""
+    _want(rows, "gate and up rows", torch.float32, contiguous=False)
+    tokens, both = rows.shape
+    if both % 2:
+        raise KernelError("gated_clamp_act: rows hold pairs")
+    if out is None:
+        out = torch.empty((tokens, both // 2), dtype=out_dtype, device=rows.device)
+    _want(out, "activated rows", _FLOAT, contiguous=False)
+    lib = core()
+    _check(lib.tge_gated_clamp_act(rows.data_ptr(), _rows_2d(rows, "gate and up rows"), out.data_ptr(),
+                                   _rows_2d(out, "activated rows"), int(out.dtype == torch.bfloat16), tokens, both // 2,
+                                   float(limit), float(alpha), float(offset), _stream()), lib)
+    return out
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[a | b] of two float32 [T, H] tensors, in ``out_dtype``."""
+    _want(a, "rows", torch.float32)
+    _want(b, "rows", torch.float32)
+    if a.shape != b.shape:
+        raise KernelError("concat_rows: shapes differ")
+    out = torch.empty((a.shape[0], 2 * a.shape[1]), dtype=out_dtype, device=a.device)
+    lib = core()
+    _check(lib.tge_concat_rows(a.data_ptr(), b.data_ptr(), out.data_ptr(), int(out_dtype == torch.bfloat16), a.shape[0],
+                               a.shape[1], _stream()), lib)
+    return out

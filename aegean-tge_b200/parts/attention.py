@@ -29,9 +29,22 @@ window and the block in the making have passed them.  Either option, or a
 rotation with values of another size than the keys, takes the general path:
 product, then one kernel that convolves, normalises, rotates and stores,
 one that pools, and the attention.
+
+Three more, which go together (the *keyed* path): the values are the keys as
+projected (``values: "keys"``: no value weight; with a q/k norm the values are
+the keys from before it, so both are stored); a temperature on the queries
+that grows with the position (``q_temp``: q times 1 + coef ln(floor((p + 1) /
+every) + 1)); and a learned bias by distance (``distance_bias``), a table
+[rows, heads] added unscaled to the scaled scores: distances below rows/2
+have a row each, beyond that the rows are spaced evenly in the logarithm up
+to ``far``, where the last row is reached and kept.  Product of q and k with
+the biases, one kernel that stores the values, normalises, applies the
+temperature and stores the keys, then the attention with the bias expanded
+to one entry per distance.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional
 
 import torch
@@ -53,6 +66,9 @@ class GQAttention(Mixer):
     weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``; ``q_norm.weight`` / ``k_norm.weight``
     (float32, the projection's or one head's size); ``sink`` [heads]; ``value_mix.weight`` (a scalar);
     ``q|k|v.conv.weight`` (float32 [channels, taps]).
+    The keyed path: ``values`` (``"own"``, the default, or ``"keys"``: no ``v.weight`` / ``v.bias``), ``q_temp`` (None
+    or ``{"coef": c, "every": n}``), ``distance_bias`` (None or ``{"far": D}``; weight ``rel`` float32 [rows, heads], the
+    rows taken from the tensor).
     """
     graph_safe = True
     can_defer_norm = True
@@ -85,6 +101,17 @@ class GQAttention(Mixer):
         self.value_mix_key = ("value_mix", str(p.get("value_mix_key", "values")))
         if self.value_dim <= 0:
             raise ValueError("attention: value_dim must be positive")
+        self.values_are_keys = str(p.get("values", "own")) == "keys"
+        if str(p.get("values", "own")) not in ("own", "keys"):
+            raise ValueError(f"attention: values {p.get('values')!r} are 'own' or 'keys'")
+        temp, dist = p.get("q_temp"), p.get("distance_bias")
+        self.q_temp = None if temp is None else (float(temp["coef"]), int(temp["every"]))
+        self.dist_far = None if dist is None else float(dist["far"])
+        if self.q_temp is not None and self.q_temp[1] <= 0:
+            raise ValueError("attention: q_temp.every must be positive")
+        if (self.q_temp is not None or self.dist_far is not None) and not self.values_are_keys:
+            raise ValueError("attention: a query temperature and a bias by distance are built for values that are the keys")
+        self.dist_table: Optional[torch.Tensor] = None
         self.taps = int(p.get("short_conv") or 0)
         self.pool = int(p.get("pool") or 0)
         if self.taps < 0 or self.taps > 16:
@@ -99,9 +126,16 @@ class GQAttention(Mixer):
         self.v_dim = self.kv_heads * self.value_dim
         self.o_dim = self.heads * self.value_dim
         # the plain layer: rotation, store and attention as the fused kernels know them
-        self.plain = self.qk_norm is None and self.value_mix is None and self.value_dim == self.head_dim
+        self.plain = (self.qk_norm is None and self.value_mix is None and self.value_dim == self.head_dim
+                      and not self.values_are_keys)
         tables = self.position.rotary_tables()
         self.rotates = tables is None or tables[2] > 0
+        if self.values_are_keys:
+            if (self.value_dim != self.head_dim or self.rotates or self.value_mix is not None or self.taps or self.pool
+                    or p.get("prepare_in_one_kernel") or (self.qk_norm is not None and self.qk_norm[0] != "head")):
+                raise ValueError("attention: values that are the keys go with equal sizes, no rotation, a per-head q/k norm "
+                                 "or none, and neither convolution, pooled blocks nor value mixing")
+            self.v_dim = 0
         # the general path: convolution, per-head norm, rotation and store in one kernel, pooled blocks
         self.general = bool(p.get("prepare_in_one_kernel") or self.taps or self.pool
                             or (self.value_dim != self.head_dim and self.rotates))
@@ -130,6 +164,10 @@ class GQAttention(Mixer):
             "v.weight": ParamSpec((self.v_dim, self.hidden)),
             "o.weight": ParamSpec((self.hidden, self.o_dim)),
         }
+        if self.values_are_keys:
+            del specs["v.weight"]
+        if self.dist_far is not None:
+            specs["rel"] = ParamSpec((-1, self.heads), role="vector")
         if self.qk_norm is not None:
             per_head = self.qk_norm[0] == "head"
             specs["q_norm.weight"] = ParamSpec((self.head_dim if per_head else self.q_dim,), role="vector")
@@ -147,16 +185,20 @@ class GQAttention(Mixer):
         if self.qkv_bias:
             specs["q.bias"] = ParamSpec((self.q_dim,), role="vector")
             specs["k.bias"] = ParamSpec((self.kv_dim,), role="vector")
-            specs["v.bias"] = ParamSpec((self.v_dim,), role="vector")
+            if not self.values_are_keys:
+                specs["v.bias"] = ParamSpec((self.v_dim,), role="vector")
         if self.o_bias:
             specs["o.bias"] = ParamSpec((self.hidden,), role="vector")
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         # rows of q, then k, then v: one product serves all three
-        self.w_qkv = torch.cat([tensors["q.weight"], tensors["k.weight"], tensors["v.weight"]], dim=0).contiguous()
+        rows = ("q", "k") if self.values_are_keys else ("q", "k", "v")
+        self.w_qkv = torch.cat([tensors[f"{t}.weight"] for t in rows], dim=0).contiguous()
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors["q.bias"], tensors["k.bias"], tensors["v.bias"]]).contiguous()
+            self.b_qkv = torch.cat([tensors[f"{t}.bias"] for t in rows]).contiguous()
+        if self.dist_far is not None:
+            self.dist_table = self.expand_distance_bias(tensors["rel"], self.dist_far)
         self.w_o = tensors["o.weight"].contiguous()
         self.b_o = tensors["o.bias"].contiguous() if self.o_bias else None
         if self.qk_norm is not None:
@@ -170,9 +212,54 @@ class GQAttention(Mixer):
         if self.value_mix == "blend":
             self.mix_w = tensors["value_mix.weight"].reshape(1).contiguous()
 
+    @staticmethod
+    def distance_row(n: int, rows: int, far: float) -> int:
+        """The table row of distance n: n itself below rows/2; beyond, rows/2 + floor(ln(n / (rows/2)) / ln(far /
+        (rows/2)) * (rows - rows/2)), and never past the last row."""
+        half = rows // 2
+        if n < half:
+            return n
+        return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+    @classmethod
+    def expand_distance_bias(cls, rel: torch.Tensor, far: float) -> torch.Tensor:
+        """``rel`` [rows, heads] -> float32 [heads, span], one entry per distance up to the first that reaches the last
+        row (every larger distance shares it): what the attention kernels index by min(distance, span - 1)."""
+        rows = rel.shape[0]
+        if rows < 2 or rows % 2 or not far > rows // 2:
+            raise ValueError(f"attention: a bias by distance needs an even number of rows (got {rows}) and far > rows/2 (got {far})")
+        picks = []
+        n = 0
+        while True:
+            picks.append(cls.distance_row(n, rows, far))
+            if picks[-1] == rows - 1:
+                break
+            n += 1
+        index = torch.tensor(picks, dtype=torch.long, device=rel.device)
+        return rel.float()[index].t().contiguous()
+
     def flops(self, tokens: int, pairs: float) -> float:
         products = 2.0 * tokens * (self.q_dim + self.kv_dim + self.v_dim + self.o_dim) * self.hidden
         return products + 2.0 * self.heads * (self.head_dim + self.value_dim) * pairs     # scores and weighted values
+
+    def attend_keyed(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Product of q and k; values stored, q and k normalised, temperature, keys stored; attention."""
+        ops = self.ops
+        complete = getattr(h, "complete", None)
+        if complete is not None:
+            h = complete()
+        k_pages, v_pages = cache.paged["k"], cache.paged["v"]
+        table = ctx.block_tables[cache.group]
+        qk = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
+        coef, every = self.q_temp if self.q_temp is not None else (0.0, 0)
+        ops.qk_temp_store(qk, self.q_norm_w, self.k_norm_w, self.qk_norm[1] if self.qk_norm else 1.0, coef, every,
+                          ctx.positions, ctx.seq_of_token, table if cache.owner else None, k_pages if cache.owner else None,
+                          v_pages if cache.owner else None, self.heads, self.kv_heads, self.head_dim)
+        return ops.attention(qk[:, :self.q_dim], k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions,
+                             ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads, self.kv_heads,
+                             self.head_dim, self.scale, window=int(self.window or 0), split_tokens=ctx.attn_split_tokens,
+                             typical_ctx_len=ctx.typical_ctx_len, decode_prefix=ctx.decode_prefix, sink=self.sink, out=out,
+                             dist_bias=self.dist_table)
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         # with pooled blocks a token is also read when its block is averaged, which is when the block's last token
@@ -223,7 +310,7 @@ class GQAttention(Mixer):
         multiplied together with q, k and v.  A mixer whose small-batch kernel can carry them (whole-projection
         q/k norm, no rotation, no biases) puts them below its own rows in one tensor and returns the view that now
         holds them (the caller uses it in place of its copy); None: it cannot."""
-        if (self.plain or self.general or self.rotates or self.qkv_bias
+        if (self.plain or self.general or self.values_are_keys or self.rotates or self.qkv_bias
                 or (self.qk_norm is not None and self.qk_norm[0] != "projection")):
             return None
         if self.w_qkv is None or rows.dtype != self.w_qkv.dtype or rows.shape[1] != self.hidden:
@@ -239,8 +326,8 @@ class GQAttention(Mixer):
 
         ``beside``: (output view, epilogue) for the rows that :meth:`share_input_projection` took in; the result is
         then a pair (rows, whether the shared rows were multiplied and activated here)."""
-        if self.general:
-            a = self.attend_general(h, ctx, cache, out=out)
+        if self.general or self.values_are_keys:
+            a = (self.attend_keyed if self.values_are_keys else self.attend_general)(h, ctx, cache, out=out)
             return a if beside is None else (a, False)
         ops = self.ops
         k_pages, v_pages = cache.paged["k"], cache.paged["v"]

@@ -37,12 +37,18 @@ class ParamSpec:
     role "matrix": operand of a matrix product or an embedding table; held in
     the run dtype (bfloat16 or float32).  role "vector": norm weight or bias;
     always held in float32 (a vector stored in 32-bit stays so, one stored in
-    bfloat16 is widened exactly).  role "table": integers, held as int32.
+    bfloat16 is widened exactly).  role "table": integers, held as int32.  An extent of -1 in ``shape`` takes
+    whatever the checkpoint's tensor has there (a table whose length no configuration key states).
     """
 
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
+
+    def takes(self, shape) -> bool:
+        """Whether a tensor of ``shape`` fits: every extent equal, or left open with -1."""
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(want in (-1, have) for want, have in zip(self.shape, shape))
 
 
 @dataclass(frozen=True)
@@ -163,7 +169,7 @@ class Part:
         for param in self.param_specs().values():
             count = 1
             for extent in param.shape:
-                count *= int(extent)
+                count *= max(int(extent), 0)          # an extent left open counts as nothing
             total += count * (self.env.dtype.itemsize if param.role == "matrix" else 4)
         return total
 
@@ -199,6 +205,14 @@ class PositionEncoding(Part):
 
     def rotary_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor, int]]:
         return None
+
+
+class StreamStep(Part):
+    """Something done to the whole stream before a layer runs (``LayerSpec.entry``): ``forward(x, x0, ctx)`` changes the
+    float32 stream ``x`` [T, H] in place; ``x0`` is the embedding output of the same tokens."""
+
+    def forward(self, x: torch.Tensor, x0: torch.Tensor, ctx: "StepContext") -> None:
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -375,6 +389,7 @@ FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+STREAM_STEPS = Registry("stream step")
 
 
 def build_part(registry: Registry, spec: PartSpec, env: BuildEnv) -> Part:

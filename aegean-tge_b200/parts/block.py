@@ -14,7 +14,8 @@ class PreNormBlock(Block):
 
     The stream ``x`` is float32 and is never itself normalised: each norm's
     output feeds the part and the part's output is added back
-    (src/models/qwen2.cpp:2055, :2099-2105, :2118).
+    (src/models/qwen2.cpp:2055, :2099-2105, :2118).  A layer without feed-forward (and then without second norm)
+    is x += mixer(norm1(x)) alone.
     """
 
     passes_deferred_rows = True
@@ -22,6 +23,10 @@ class PreNormBlock(Block):
     def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None, next_takes_deferred=False):
         if h is None:
             h = self.mixer_norm.forward(x)
+        if self.feed_forward is None:
+            if isinstance(h, self.env.ops.DeferredRows) and not self.mixer.takes_deferred_rows:
+                h = h.complete()
+            return self.mixer.forward_add(h, x, ctx, cache, next_norm=next_norm)
         # a part is only asked to leave the norm's factor to its successor if both sides say they can
         defer = {"defer": True} if self.mixer.can_defer_norm and self.feed_forward.takes_deferred_rows else {}
         h = self.mixer.forward_add(h, x, ctx, cache, next_norm=self.ffn_norm, **defer)

@@ -17,7 +17,8 @@ from .base import EMBEDDINGS, HEADS, NORMS, ParamSpec, Part, build_part
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
     """params: ``vocab_size``, ``hidden_size``; optional ``norm`` (a norm's PartSpec: the looked-up rows are
-    normalised before they become the stream; the norm needs ``forward_stream``).  weights: ``weight`` and, with a
+    normalised before they become the stream; the norm needs ``forward_stream``), ``scale`` (a factor on the looked-up
+    rows, default 1; a head that shares the table reads it unscaled).  weights: ``weight`` and, with a
     norm, its parameters as ``norm.<name>``."""
     graph_safe = True
 
@@ -25,6 +26,7 @@ class TokenEmbedding(Part):
         super().__init__(spec, env)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
         norm = spec.params.get("norm")
         self.norm = build_part(NORMS, norm, env) if norm is not None else None
@@ -46,7 +48,7 @@ class TokenEmbedding(Part):
         return 0        # a step reads the rows of its tokens, not the table
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        x = self.ops.embedding(self.weight, token_ids)
+        x = self.ops.embedding(self.weight, token_ids, scale=self.scale)
         return x if self.norm is None else self.norm.forward_stream(x)
 
 

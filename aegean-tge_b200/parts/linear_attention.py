@@ -121,6 +121,9 @@ class MixerSum(Mixer):
 
     params: ``branches``: a list of ``(name, PartSpec, scale)``.  A branch's parameters are this part's under
     ``<name>.<local name>``, its state entries likewise; at most one branch keeps pages (they become this part's).
+    Optional ``normalize`` (``{"eps": e, "hidden_size": H}``): each branch's output is first divided by its root mean
+    square over the width and multiplied by a weight of its own, out = sum_b scale_b * rms(mixer_b(h)) w_b; weights
+    ``<name>.out_norm.weight`` (float32 [H]).
     """
 
     def __init__(self, spec, env):
@@ -137,15 +140,25 @@ class MixerSum(Mixer):
             raise ValueError(f"mixer_sum: branches {paged} all keep pages; one may")
         self.paged_branch = paged[0] if paged else None
         self.graph_safe = all(mixer.graph_safe for _, mixer, _ in self.branches)
+        normalize = spec.params.get("normalize")
+        self.normalize = None if normalize is None else (float(normalize["eps"]), int(normalize["hidden_size"]))
+        self.out_norms: Dict[str, torch.Tensor] = {}
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {f"{name}.{local}": param for name, mixer, _ in self.branches
-                for local, param in mixer.param_specs().items()}
+        specs = {f"{name}.{local}": param for name, mixer, _ in self.branches
+                 for local, param in mixer.param_specs().items()}
+        if self.normalize is not None:
+            for name, _, _ in self.branches:
+                specs[f"{name}.out_norm.weight"] = ParamSpec((self.normalize[1],), role="vector")
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         for name, mixer, _ in self.branches:
             prefix = name + "."
-            mixer.load({key[len(prefix):]: t for key, t in tensors.items() if key.startswith(prefix)})
+            if self.normalize is not None:
+                self.out_norms[name] = tensors[prefix + "out_norm.weight"].contiguous()
+            mixer.load({key[len(prefix):]: t for key, t in tensors.items()
+                        if key.startswith(prefix) and key != prefix + "out_norm.weight"})
 
     def param_bytes(self) -> int:
         return sum(mixer.param_bytes() for _, mixer, _ in self.branches)
@@ -182,10 +195,31 @@ class MixerSum(Mixer):
         return view
 
     def forward_f32(self, h, ctx: StepContext, cache: LayerCache, out=None, alpha: float = 1.0, accumulate: bool = False):
+        if self.normalize is not None:
+            if out is None or not accumulate:
+                if out is None:
+                    out = torch.empty((h.shape[0], self.env.hidden_size), dtype=torch.float32, device=h.device)
+                out.zero_()
+            self.add_normalized(h, out, ctx, cache, alpha)
+            return out
         for index, (name, mixer, scale) in enumerate(self.branches):
             out = mixer.forward_f32(h, ctx, self._branch_cache(name, cache), out=out, alpha=alpha * scale,
                                     accumulate=accumulate or index > 0)
         return out
+
+    def add_normalized(self, h, x: torch.Tensor, ctx: StepContext, cache: LayerCache, alpha: float = 1.0) -> None:
+        """x += alpha * sum_b scale_b * rms(mixer_b(h)) w_b: every branch's float32 output is normalised over the width
+        and added by one kernel."""
+        eps = self.normalize[0]
+        for name, mixer, scale in self.branches:
+            y = mixer.forward_f32(h, ctx, self._branch_cache(name, cache))
+            self.ops.norm_scale_add(x, y, self.out_norms[name], eps, alpha=alpha * scale)
+
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache, next_norm=None):
+        if self.normalize is None:
+            return super().forward_add(h, x, ctx, cache, next_norm=next_norm)
+        self.add_normalized(h, x, ctx, cache)
+        return None
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.to_run_dtype(self.forward_f32(h, ctx, cache), self.env.dtype)

@@ -17,7 +17,9 @@ from .base import NORMS, Norm, ParamSpec
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """params: ``size`` (row width), ``eps``; optional ``optional`` (bool: a checkpoint may lack the weight; the norm
-    then does not exist: ``fusable()`` is None and ``forward`` refuses).  weights: ``weight``."""
+    then does not exist: ``fusable()`` is None and ``forward`` refuses); optional ``unit_offset`` (bool: the weight is
+    stored around zero and the row is multiplied by 1 + w; the sum is formed once, in float32, when the weight
+    arrives).  weights: ``weight``."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -27,6 +29,7 @@ class RMSNorm(Norm):
         if self.size <= 0 or not self.eps > 0.0:
             raise ValueError(f"rmsnorm: size {self.size} and eps {self.eps} must be positive")
         self.optional = bool(spec.params.get("optional", False))
+        self.unit_offset = bool(spec.params.get("unit_offset", False))
         self.loaded = False
         self.weight: Optional[torch.Tensor] = None
 
@@ -35,6 +38,8 @@ class RMSNorm(Norm):
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors.get("weight") if self.optional else tensors["weight"]
+        if self.unit_offset and self.weight is not None:
+            self.weight = (self.weight.float() + 1.0).contiguous()
         self.loaded = True
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -31,7 +31,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .base import FEED_FORWARDS, FeedForward, ParamSpec, StepContext
+from .base import FEED_FORWARDS, FeedForward, ParamSpec, StepContext, build_part
 
 DIRECT_MAX_TOKENS = 32      # steps of up to this many tokens (and every step of single tokens) avoid the grouped path
 DENSE_MAX_TOKENS = 256      # beyond this many tokens the wasted products of the dense path would cost more than its bytes
@@ -42,9 +42,13 @@ class RoutedExperts(FeedForward):
     """params: ``hidden_size``, ``intermediate_size`` (an expert's inner width), ``experts``, ``top``, optional
     ``identity`` (default 0), ``group_count`` / ``group_keep`` (default 1 / 1: no groups), ``correction`` (bool,
     default True: the checkpoint holds a correction of the choice), ``activation`` (``"relu_squared"``, the only one
-    the expert kernels apply so far).
-    weights: ``router.weight`` [experts + identity, hidden], ``correction`` (float32 [experts + identity]),
-    ``experts.<e>.up.weight`` [inner, hidden], ``experts.<e>.down.weight`` [hidden, inner]."""
+    the expert kernels apply so far), ``router_bias`` (bool, default False: a bias added to the router's logits, so it
+    steers the choice and the weights alike), ``shared`` (None, or the PartSpec of a feed-forward that every token
+    uses and whose output is added; its parameters are this part's under ``shared.<local name>``).
+    With no correction and no groups the weights are the softmax over the chosen logits alone: a chosen output's share
+    of the softmax over all, divided by the chosen ones' sum, is the same number.
+    weights: ``router.weight`` [experts + identity, hidden], ``router.bias`` and ``correction`` (float32 [experts +
+    identity]), ``experts.<e>.up.weight`` [inner, hidden], ``experts.<e>.down.weight`` [hidden, inner]."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -58,6 +62,12 @@ class RoutedExperts(FeedForward):
         self.group_count = int(p.get("group_count", 1))
         self.group_keep = int(p.get("group_keep", 1))
         self.has_correction = bool(p.get("correction", True))
+        self.has_router_bias = bool(p.get("router_bias", False))
+        shared = p.get("shared")
+        self.shared: Optional[FeedForward] = build_part(FEED_FORWARDS, shared, env) if shared is not None else None
+        if self.shared is not None:
+            self.graph_safe = bool(self.shared.graph_safe)
+        self.router_bias: Optional[torch.Tensor] = None
         self.outputs = self.experts + self.identity
         if str(p.get("activation", "relu_squared")) != "relu_squared":
             raise ValueError(f"routed_experts: unknown activation '{p.get('activation')}'")
@@ -79,6 +89,10 @@ class RoutedExperts(FeedForward):
         specs = {"router.weight": ParamSpec((self.outputs, self.hidden))}
         if self.has_correction:
             specs["correction"] = ParamSpec((self.outputs,), role="vector")
+        if self.has_router_bias:
+            specs["router.bias"] = ParamSpec((self.outputs,), role="vector")
+        if self.shared is not None:
+            specs.update({f"shared.{local}": param for local, param in self.shared.param_specs().items()})
         for e in range(self.experts):
             specs[f"experts.{e}.up.weight"] = ParamSpec((self.inner_size, self.hidden))
             specs[f"experts.{e}.down.weight"] = ParamSpec((self.hidden, self.inner_size))
@@ -87,6 +101,9 @@ class RoutedExperts(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.w_router = tensors["router.weight"].contiguous()
         self.correction = tensors["correction"].contiguous() if self.has_correction else None
+        self.router_bias = tensors["router.bias"].contiguous() if self.has_router_bias else None
+        if self.shared is not None:
+            self.shared.load({name[len("shared."):]: t for name, t in tensors.items() if name.startswith("shared.")})
         if self.experts:
             self.w_up = torch.stack([tensors[f"experts.{e}.up.weight"] for e in range(self.experts)]).contiguous()
             self.w_down = torch.stack([tensors[f"experts.{e}.down.weight"] for e in range(self.experts)], dim=1).contiguous()
@@ -97,7 +114,8 @@ class RoutedExperts(FeedForward):
     def param_bytes(self) -> int:
         """What one token's step reads: the router and the chosen experts (a large batch touches more of them)."""
         item = self.env.dtype.itemsize
-        return (self.outputs * self.hidden + min(self.top, self.experts) * 2 * self.inner_size * self.hidden) * item + 4 * self.outputs
+        extra = self.shared.param_bytes() if self.shared is not None else 0
+        return (self.outputs * self.hidden + min(self.top, self.experts) * 2 * self.inner_size * self.hidden) * item + 4 * self.outputs + extra
 
     def dense(self, tokens: int) -> bool:
         """Whether a step of this many tokens runs all experts (its choices reach most of them anyway)."""
@@ -108,21 +126,31 @@ class RoutedExperts(FeedForward):
         uniform choices would reach on average."""
         item = self.env.dtype.itemsize
         reached = self.experts if self.dense(tokens) else self.experts * (1.0 - (1.0 - min(self.top / self.outputs, 1.0)) ** tokens)
-        return int((self.outputs * self.hidden + reached * 2 * self.inner_size * self.hidden) * item) + 4 * self.outputs
+        extra = self.shared.param_bytes() if self.shared is not None else 0
+        return int((self.outputs * self.hidden + reached * 2 * self.inner_size * self.hidden) * item) + 4 * self.outputs + extra
 
     def flops(self, tokens: int, pairs: float) -> float:
-        return 2.0 * tokens * (self.outputs * self.hidden + self.top * 2 * self.inner_size * self.hidden)
+        extra = self.shared.flops(tokens, pairs) if self.shared is not None else 0.0
+        return 2.0 * tokens * (self.outputs * self.hidden + self.top * 2 * self.inner_size * self.hidden) + extra
 
     def route(self, h: torch.Tensor):
         """(ids int32 [T, top], weights float32 [T, top]); the logits are a float32 product of the rows as given."""
         complete = getattr(h, "complete", None)
         if complete is not None:
             h = complete()
-        logits = self.ops.linear(h, self.w_router, None, self.ops.GEMM_STORE_F32)
+        logits = self.ops.linear(h, self.w_router, self.router_bias, self.ops.GEMM_STORE_F32)
         ids, weights = self.ops.router_topk(logits, self.correction, self.top, self.group_count, self.group_keep)
         return h, ids, weights
 
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None):
+        h = self.add_routed(h, x, ctx)
+        if self.shared is not None:
+            # the feed-forward every token uses adds last, and with it whatever it can do for the next norm
+            return self.shared.forward_add(h, x, ctx, next_norm=next_norm)
+        return None
+
+    def add_routed(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """Adds the chosen experts' weighted outputs into ``x``; returns the rows as the experts read them."""
         ops = self.ops
         h, ids, weights = self.route(h)
         tokens = h.shape[0]
@@ -131,10 +159,10 @@ class RoutedExperts(FeedForward):
             z = ops.linear(h, self.w_up.view(self.experts * self.inner_size, self.hidden), None, ops.GEMM_STORE)
             ops.experts_dense_weigh(z, ids, weights, h, x, self.experts)
             ops.linear(z, self.w_down.view(self.hidden, self.experts * self.inner_size), None, ops.GEMM_ADD_F32, out=x)
-            return None
+            return h
         if few or self.experts == 0:
             ops.experts_direct(h, self.w_up, self.w_down, ids, weights, x)
-            return None
+            return h
         place, offsets, grouped = ops.experts_group(h, ids, self.experts)
         bounds: List[int] = offsets.tolist()             # the host learns the group sizes: not a captured step
         rows = bounds[-1]
@@ -151,7 +179,7 @@ class RoutedExperts(FeedForward):
             if hi > lo:
                 ops.linear(inner[lo:hi], self.w_down[:, e, :], None, ops.GEMM_STORE_F32, out=outputs[lo:hi])
         ops.experts_combine_add(outputs, place, weights, h, x)
-        return None
+        return h
 
     def forward_f32(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         out = torch.zeros((h.shape[0], self.hidden), dtype=torch.float32, device=h.device)

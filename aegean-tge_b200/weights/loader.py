@@ -66,7 +66,7 @@ def check_against_manifest(entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...]
         if name not in entries:
             continue
         dtype, shape = entries[name]
-        if tuple(shape) != tuple(param.shape):
+        if not param.takes(shape):
             mismatched.append(f"{name}: file has shape {list(shape)}, {where} needs {list(param.shape)}")
         elif param.role == "table" and dtype not in _INTS:
             mismatched.append(f"{name}: file has {dtype}, {where} needs integers")
@@ -161,7 +161,7 @@ def load_tensors(model, named_tensors) -> None:
     seen: Dict[str, Tuple[torch.dtype, Tuple[int, ...]]] = {}
     for name, value in named_tensors:
         seen[name] = (value.dtype, tuple(value.shape))
-        if name in manifest and tuple(value.shape) == tuple(manifest[name][0].shape):
+        if name in manifest and manifest[name][0].takes(value.shape):
             tensors[name] = value.to(device=env.device, dtype=device_dtype(manifest[name][0], env.dtype)).contiguous()
     check_against_manifest(seen, manifest)
     model.load(tensors)
