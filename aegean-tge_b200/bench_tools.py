@@ -223,7 +223,32 @@ def paired_configs(width: int, heads: int, kv_heads: int, head_dim: int, gated_i
     lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
                "logit_scale": 1.0, "logit_softcap": 50.0, "layers": [layer] * layers}
     return {"qwen2": qwen2, "lepizen": lepizen, "mozepel": mozepel_config(width, heads, kv_heads, head_dim, gated_inner, layers, vocab),
-            "puputar": puputar_config(width, heads, head_dim, gated_inner, layers, vocab)}
+            "puputar": puputar_config(width, heads, head_dim, gated_inner, layers, vocab),
+            "kokolorn": kokolorn_config(width, heads, kv_heads, head_dim, gated_inner, layers, vocab)}
+
+
+def kokolorn_config(width: int, heads: int, kv_heads: int, head_dim: int, gated_inner: int, layers: int, vocab: int,
+                    experts: int = 16, top: int = 4) -> dict:
+    """A Kokolorn config.json with the width, heads, kv heads, head size and layer count of a Qwen2 shape, its layers by
+    turns delta (keys and values of ``head_dim``, four taps, the clamped gated feed-forward of the gated inner width),
+    attention (the shape's GQA; ``experts`` experts of a quarter of the gated inner width of which ``top`` are used, and
+    a shared one of half of it: as many multiplications per token as the dense one), parallel (the shape's GQA with a
+    bias by distance up to 2,048 beside a state-space mixer of as many heads, states of 128 rows, four taps) and
+    attention again; one pass over all layers, so the stream is mixed with the embedding once."""
+    quarter = max(gated_inner // 4 // 64 * 64, 64)
+    dense = {"kind": "dense", "ff": gated_inner, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": quarter}, "router": {"experts": experts, "top": top}, "shared": {"ff": 2 * quarter}}
+    temp = {"coef": 0.1, "every": 1024}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "q_temp": temp}
+    kinds = [
+        {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4}, "mlp": dense},
+        {"type": "attention", "mixer": dict(attention), "mlp": moe},
+        {"type": "parallel", "mixer": {"left": dict(attention, bias_max=2048.0),
+                                       "right": {"heads": heads, "vdim": head_dim, "state": 128, "groups": kv_heads,
+                                                 "norm_groups": kv_heads, "conv": 4}}, "mlp": moe},
+        {"type": "attention", "mixer": dict(attention), "mlp": moe}]
+    return {"architecture": "Kokolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [kinds[n % 4] for n in range(layers)], "loop": {"start": 0, "stop": layers, "times": 1}}
 
 
 def puputar_config(width: int, heads: int, head_dim: int, gated_inner: int, layers: int, vocab: int, experts: int = 16,

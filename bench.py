@@ -15,9 +15,10 @@ portion), the same figures with the engine's default pages of 64 tokens, long
 contexts, and the 14B and 32B shapes.  This engine runs on one GPU: for --gpus
 above 1 it says so and exits with 2.
 
-    python bench.py --compare lepizen|mozepel|puputar [--compare-sizes 7b,14b,1.5b] [--steps K] [--compare-timelines first|all|none]
+    python bench.py --compare lepizen|mozepel|puputar|kokolorn [--compare-sizes 7b,14b,1.5b] [--steps K] [--compare-timelines first|all|none]
 
-is another measurement and leaves the one above alone: the Lepizen, Mozepel or Puputar design beside the Qwen2 design at
+is another measurement and leaves the one above alone: the Lepizen, Mozepel, Puputar or Kokolorn design beside the Qwen2 design
+(Kokolorn also beside Mozepel, the design whose layers are most like its own) at
 equal width, heads, layers and vocabulary (Lepizen: and parameter count), at sizes of real models' layers (random weights),
 prefill and decode, with the kernels of one step of each at the first size (or all sizes).  It prints one JSON line
 {"compare": ...}.
@@ -153,7 +154,7 @@ COMPARE_SIZES = {"1.5b": (1536, 12, 2, 128, 8960), "7b": (3584, 28, 4, 128, 1894
 
 
 def compare(args) -> int:
-    """`--compare lepizen`, `mozepel` or `puputar`: Qwen2 and that design at each size, one JSON line."""
+    """`--compare lepizen`, `mozepel`, `puputar` or `kokolorn`: Qwen2 and that design at each size, one JSON line."""
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -165,13 +166,14 @@ def compare(args) -> int:
             print(f"bench.py: --compare-sizes knows {', '.join(COMPARE_SIZES)}, not '{size}'")
             return 2
     peak, source = peaks.load()
-    out = {"designs": ["qwen2", args.compare], "layers": args.compare_layers, "prompt": PROMPT, "dtype": "bf16",
+    beside = ("qwen2", "mozepel") if args.compare == "kokolorn" else ("qwen2",)
+    out = {"designs": [*beside, args.compare], "layers": args.compare_layers, "prompt": PROMPT, "dtype": "bf16",
            "data": "synthetic: random weights seed 0, uniform random token ids", "peaks": peak, "peaks_source": source,
            "sizes": {}}
     for size in sizes:
         width, heads, kv_heads, head_dim, inner = COMPARE_SIZES[size]
         configs = paired_configs(width, heads, kv_heads, head_dim, inner, args.compare_layers, CONFIG_7B["vocab_size"])
-        configs = {name: configs[name] for name in ("qwen2", args.compare)}
+        configs = {name: configs[name] for name in (*beside, args.compare)}
         timelines = args.compare_timelines == "all" or (args.compare_timelines == "first" and size == sizes[0])
         out["sizes"][size] = compare_designs(configs, prompt_len=PROMPT, steps=min(args.steps, 32), warmup=max(args.warmup, 3),
                                              timelines=timelines)
@@ -189,7 +191,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=CONFIG_7B["num_hidden_layers"],
                         help="fewer layers than the model has, if memory or time needs it (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="the headline only: no points")
-    parser.add_argument("--compare", choices=["lepizen", "mozepel", "puputar"], help="instead of the headline: this design beside Qwen2 at equal size")
+    parser.add_argument("--compare", choices=["lepizen", "mozepel", "puputar", "kokolorn"], help="instead of the headline: this design beside Qwen2 at equal size")
     parser.add_argument("--compare-sizes", default="7b,14b,1.5b", help="which of 1.5b, 7b, 14b (layer shapes), with commas")
     parser.add_argument("--compare-layers", type=int, default=8, help="layers of each model in --compare")
     parser.add_argument("--compare-timelines", choices=["first", "all", "none"], default="first",

@@ -84,12 +84,14 @@ def softmax_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float,
     T, H, _ = q.shape
     G = k.shape[1]
     out = np.zeros((T, H, v.shape[2]), dtype=F)
+    if bias is not None:                                   # by_distance[h, n]: the bias of the key n positions back
+        by_distance = np.array([[bias[distance_bucket(n, bias.shape[0], far), h] for n in range(T)] for h in range(H)], dtype=F)
     for h in range(H):
         g = h // (H // G)
         for i in range(T):
             s = (k[:i + 1, g] @ q[i, h]) * scale
             if bias is not None:
-                s = s + np.array([bias[distance_bucket(i - j, bias.shape[0], far), h] for j in range(i + 1)], dtype=F)
+                s = s + by_distance[h, i::-1]
             w = np.exp(s - s.max())
             out[i, h] = (w / w.sum()) @ v[:i + 1, g]
     return out.reshape(T, -1)
@@ -103,7 +105,8 @@ def attention_mixer(h: np.ndarray, W: Dict[str, np.ndarray], p: str, m: dict, ep
     v = k.copy()                                           # the values are the keys as projected
     q = rms_norm(q, W[p + "q.norm"], eps)
     k = rms_norm(k, W[p + "k.norm"], eps)
-    q = q * query_temperature(np.arange(T), m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    if m.get("q_temp") is not None:
+        q = q * query_temperature(np.arange(T), m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
     a = softmax_attention(q, k, v, m["scale"])
     return a @ W[p + "o"].astype(F).T
 
@@ -176,7 +179,8 @@ def biased_attention_mixer(h: np.ndarray, W: Dict[str, np.ndarray], p: str, m: d
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ W[p + "q"].astype(F).T + W[p + "q.b"].astype(F)).reshape(T, H, d)
     k = (h @ W[p + "k"].astype(F).T + W[p + "k.b"].astype(F)).reshape(T, G, d)
-    q = q * query_temperature(np.arange(T), m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    if m.get("q_temp") is not None:
+        q = q * query_temperature(np.arange(T), m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
     a = softmax_attention(q, k, k, m["scale"], bias=W[p + "rel"].astype(F), far=float(m["bias_max"]))
     return a @ W[p + "o"].astype(F).T + W[p + "o.b"].astype(F)
 
@@ -197,17 +201,21 @@ def expert(h: np.ndarray, W: Dict[str, np.ndarray], p: str) -> np.ndarray:
     return np.maximum(h @ W[p + "up"].astype(F).T, 0.0) ** 2 @ W[p + "down"].astype(F).T
 
 
-def route(h: np.ndarray, W: Dict[str, np.ndarray], p: str, top: int):
-    """(chosen experts [T, top], weights [T, top]): the largest logits, softmax over them alone."""
+def route(h: np.ndarray, W: Dict[str, np.ndarray], p: str, top: int, margins: Optional[list] = None):
+    """(chosen experts [T, top], weights [T, top]): the largest logits, softmax over them alone.  ``margins`` collects,
+    per token, how far the last chosen logit lies above the first one left out."""
     z = h @ W[p + "router"].astype(F).T + W[p + "router.b"].astype(F)
     ids = np.argsort(-z, axis=-1, kind="stable")[:, :top]
+    if margins is not None:
+        ordered = -np.sort(-z, axis=-1)
+        margins.append(ordered[:, top - 1] - ordered[:, top] if z.shape[1] > top else np.full(z.shape[0], np.inf))
     zs = np.take_along_axis(z, ids, axis=-1)
     w = np.exp(zs - zs.max(-1, keepdims=True))
     return ids, w / w.sum(-1, keepdims=True)
 
 
-def moe_ff(h: np.ndarray, W: Dict[str, np.ndarray], p: str, mlp: dict) -> np.ndarray:
-    ids, w = route(h, W, p, mlp["router"]["top"])
+def moe_ff(h: np.ndarray, W: Dict[str, np.ndarray], p: str, mlp: dict, margins: Optional[list] = None) -> np.ndarray:
+    ids, w = route(h, W, p, mlp["router"]["top"], margins)
     out = np.zeros((h.shape[0], W[p + "e0.down"].shape[0]), dtype=F)
     for t in range(h.shape[0]):
         for j in range(ids.shape[1]):
@@ -229,7 +237,8 @@ def run_order(config: dict) -> List[tuple]:
     return order + [(n, None) for n in range(loop["stop"], count)]
 
 
-def layer_forward(x: np.ndarray, W: Dict[str, np.ndarray], n: int, layer: dict, eps: float) -> np.ndarray:
+def layer_forward(x: np.ndarray, W: Dict[str, np.ndarray], n: int, layer: dict, eps: float,
+                  margins: Optional[list] = None) -> np.ndarray:
     p = f"l{n}."
     h = layer_norm(x, W[p + "norm1"], eps)
     kind = layer["type"]
@@ -247,19 +256,21 @@ def layer_forward(x: np.ndarray, W: Dict[str, np.ndarray], n: int, layer: dict, 
     h = layer_norm(x, W[p + "norm2"], eps)
     if mlp["kind"] == "dense":
         return x + dense_ff(h, W, p + "mlp.", mlp["limit"])
-    return x + moe_ff(h, W, p + "mlp.", mlp)
+    return x + moe_ff(h, W, p + "mlp.", mlp, margins)
 
 
-def forward(config: dict, W: Dict[str, np.ndarray], tokens, streams: Optional[list] = None) -> np.ndarray:
-    """Logits [T, vocab] of one sequence; ``streams`` collects the stream after every layer run."""
+def forward(config: dict, W: Dict[str, np.ndarray], tokens, streams: Optional[list] = None,
+            margins: Optional[list] = None) -> np.ndarray:
+    """Logits [T, vocab] of one sequence; ``streams`` collects the stream after every layer run, ``margins`` every
+    routed layer run's distances from another choice of experts."""
     eps = config["norm"]["eps"]
     E = W["embed"].astype(F)
-    x0 = E[np.asarray(tokens)] * config["embedding"]["scale"]
+    x0 = E[np.asarray(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     x = x0.copy()
     for n, opens in run_order(config):
         if opens is not None:
             x = np.concatenate([x, x0], axis=-1) @ W["loop.in"].astype(F).T + W["loop.step"].astype(F)[opens]
-        x = layer_forward(x, W, n, config["layers"][n], eps)
+        x = layer_forward(x, W, n, config["layers"][n], eps, margins)
         if streams is not None:
             streams.append(x.copy())
     return layer_norm(x, W["final.norm"], eps) @ E.T
