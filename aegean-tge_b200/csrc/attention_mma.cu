@@ -54,6 +54,9 @@ struct AttnParams {
   const int* q_start;
   const int* start_pos;
   const float* sink;         // null, or one score per query head that joins the denominator once, unscaled
+  const float* dist_bias;    // null, or [heads, dist_span]: a learned bias by distance, added unscaled to the scaled scores
+  int dist_span;             // distances from dist_span - 1 on share the row's last entry
+  float bias_to_raw;         // 1 / scale: the bias in the units of an unscaled score
   __nv_bfloat16* out;
   float* partial_o;
   float* partial_ml;
@@ -70,6 +73,11 @@ struct AttnParams {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// The bias of `head` for the key `distance` positions back, in base-2 units like a scaled score.
+__device__ __forceinline__ float distance_bias(const AttnParams& p, int head, int distance) {
+  return p.dist_bias[(size_t)head * p.dist_span + min(max(distance, 0), p.dist_span - 1)] * LOG2E;
+}
 
 // The denominator `l` (relative to the running maximum `m_log2`, in base-2 units) with the head's sink in it.
 // exp2(sink - m) may overflow to +inf when every score lies far below the sink: the row's output is then 0,
@@ -260,7 +268,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         for (int e = 0; e < 2; ++e) {
           const int kpos = k0 + n * 8 + 2 * t4 + e;
           const bool visible = row_valid[i] && kpos <= row_pos[i] && kpos >= first_key && kpos >= lo && kpos < hi;
-          const float s = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          float s = -INFINITY;
+          if (visible) {
+            s = s_acc[n][2 * i + e] * p.scale_log2;
+            if (p.dist_bias != nullptr) s += distance_bias(p, row_head[i], row_pos[i] - kpos);
+          }
           s_acc[n][2 * i + e] = s;
           mx = fmaxf(mx, s);
         }
@@ -458,7 +470,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
         for (int e = 0; e < 2; ++e) {
           const int kpos = k0 + n * 8 + 2 * t4 + e;
           const bool visible = row_valid && kpos >= lo && kpos < hi;
-          const float sv = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          float sv = -INFINITY;
+          if (visible) {
+            sv = s_acc[n][2 * i + e] * p.scale_log2;
+            if (p.dist_bias != nullptr) sv += distance_bias(p, kvh * p.group + g8 + 8 * i, pos - kpos);
+          }
           s_acc[n][2 * i + e] = sv;
           mx = fmaxf(mx, sv);
         }
@@ -772,7 +788,11 @@ __global__ void __launch_bounds__((4 * GROUPS + 1) * 32) attention_decode_tma_ke
         for (int e = 0; e < 2; ++e) {
           const int kpos = k0 + n * 8 + 2 * t4 + e;
           const bool visible = row_valid && kpos >= lo && kpos < hi;
-          const float sv = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          float sv = -INFINITY;
+          if (visible) {
+            sv = s_acc[n][2 * i + e] * p.scale_log2;
+            if (p.dist_bias != nullptr) sv += distance_bias(p, kvh * p.group + g8 + 8 * i, pos - kpos);
+          }
           s_acc[n][2 * i + e] = sv;
           mx = fmaxf(mx, sv);
         }
@@ -1061,6 +1081,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           float sv = s_acc[n][2 * i + e] * p.scale_log2;
+          if (p.dist_bias != nullptr) sv += distance_bias(p, row_head[i], row_pos[i] - (k0 + n * 8 + 2 * t4 + e));
           if (!clean) {
             const int kpos = k0 + n * 8 + 2 * t4 + e;
             const bool visible = row_valid[i] && kpos <= row_pos[i] && kpos >= first_key && kpos >= lo && kpos < hi;
@@ -1316,8 +1337,10 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int first_token, const float* sink, int leave_states, int v_pitch, cudaStream_t stream) {
+                              int first_token, const float* sink, int leave_states, int v_pitch, const float* dist_bias,
+                              int dist_span, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
+  TGE_REQUIRE(dist_bias == nullptr || (dist_span > 0 && scale != 0.0f), "attention_mma: a bias by distance needs its span");
   TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
   const int group = heads / kv_heads;
@@ -1333,6 +1356,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
   p.block_table = block_table; p.q_start = q_start; p.start_pos = start_pos;
   p.out = (__nv_bfloat16*)out; p.status = status; p.sink = sink;
+  p.dist_bias = dist_bias; p.dist_span = dist_span; p.bias_to_raw = dist_bias != nullptr ? 1.0f / scale : 0.0f;
   p.leave_states = leave_states;
   if (v_pitch == 0) v_pitch = DV;
   TGE_REQUIRE(v_pitch >= DV && v_pitch % 8 == 0, "attention_mma: a value pitch of %d (values of %d) must be a multiple of 8", v_pitch, DV);
@@ -1537,13 +1561,15 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
 // sequence's keys once for all query heads of a kv head, instead of filling one 128-row query tile of the
 // prefill kernel each; the other sequences follow in a second launch.  A row's value does not depend on the
 // route beyond rounding.
+// `dist_bias` (float32 [heads, dist_span], or null): a learned bias by distance, added unscaled to the scaled score of the
+// key n positions back, entry min(n, dist_span - 1) of the head's row; every kernel adds it where it scales its scores.
 TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                               const int* block_table, int max_pages, int num_pages, int page_size,
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
                               int decode_prefix, int prefix_split_tokens, const float* sink, int leave_states,
-                              int v_pitch, cudaStream_t stream) {
+                              int v_pitch, const float* dist_bias, int dist_span, cudaStream_t stream) {
   TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
               decode_prefix, num_seqs);
   TGE_REQUIRE(prefix_split_tokens >= 0 && prefix_split_tokens % BKV == 0,
@@ -1551,14 +1577,16 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
     return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
                               positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
-                              window, split_tokens, scratch, status, 0, sink, leave_states, v_pitch, stream);
+                              window, split_tokens, scratch, status, 0, sink, leave_states, v_pitch, dist_bias, dist_span, stream);
   const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
                                        start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
-                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, leave_states, v_pitch, stream);
+                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, leave_states, v_pitch, dist_bias,
+                                       dist_span, stream);
   if (first < 0) return first;
   const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
                                       num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,
                                       num_seqs - decode_prefix, tokens, max_q_len, max_ctx_len, out, out_stride, heads,
-                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, leave_states, v_pitch, stream);
+                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, leave_states, v_pitch, dist_bias,
+                                      dist_span, stream);
   return rest < 0 ? rest : first + rest;
 }

@@ -310,6 +310,21 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       load32(s_now + lane_base, s_bits);
       load32(s_now + lane_base + 32, s_bits + 32);
       wait_loads();
+      if (p.dist_bias != nullptr) {
+        // the bias by distance, in the units of an unscaled score; a tile that lies wholly beyond the distance at which
+        // the table stops changing gets one number
+        const float* bias_row = p.dist_bias + (size_t)row_head * p.dist_span;
+        const int d0 = row_pos - k0;                       // the distance of the tile's first key
+        if (d0 - (BKV - 1) >= p.dist_span - 1) {
+          const float far = bias_row[p.dist_span - 1] * p.bias_to_raw;
+#pragma unroll
+          for (int j = 0; j < BKV; ++j) s_bits[j] = __float_as_uint(__uint_as_float(s_bits[j]) + far);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BKV; ++j)
+            s_bits[j] = __float_as_uint(fmaf(bias_row[min(max(d0 - j, 0), p.dist_span - 1)], p.bias_to_raw, __uint_as_float(s_bits[j])));
+        }
+      }
       // a tile that every row of the warp sees whole needs no mask
       // (rows beyond the tile's queries hold zeros and are never stored: they need none either)
       const bool whole = !row_valid || (k0 + BKV - 1 <= row_pos && k0 >= first_key && k0 >= lo && k0 + BKV <= hi);

@@ -219,11 +219,145 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_kernel(
   }
 }
 
+// The same recurrence for portions of several tokens and keys of 32, 64, 128 or 256 numbers: q, k, v and the gates of
+// 16 tokens (8 with keys of 256) are copied into shared memory ahead of the arithmetic (cp.async, two buffers), so that a token's
+// step waits for shared memory and three butterfly steps, not for the L2.  A lane holds the ROWS consecutive rows
+// part * ROWS .. of its column, read as 16-byte units; the parts' runs are four floats apart in banks.
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int ROWS, bool DELTA>
+__global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
+    const float* __restrict__ qk, const float* __restrict__ v, const float* __restrict__ gates,
+    const float* __restrict__ skip, int heads, int groups, int vdim, float* __restrict__ state,
+    const int* __restrict__ slots, const int* __restrict__ q_start, float* __restrict__ out) {
+  constexpr int DIM = ROWS * 8;
+  constexpr int GS_TOKENS = ROWS > 16 ? 8 : 16;       // tokens per buffer: both buffers within 48 KB
+  constexpr int PITCH = ROWS + 4;                      // floats between two parts' runs
+  constexpr int VEC = 2 * 8 * PITCH;                   // q then k of one token
+  __shared__ __align__(16) float qk_s[2][GS_TOKENS][VEC];
+  __shared__ float v_s[2][GS_TOKENS][GR_COLS];
+  __shared__ __align__(8) float g_s[2][GS_TOKENS][2];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = lane & 7;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int group = head / (heads / groups);
+  const int local = warp * 4 + (lane >> 3);
+  const int column = blockIdx.x * GR_COLS + local;
+  const bool live = column < vdim;
+  const int first = q_start[seq], last = q_start[seq + 1];
+  const int slot = slots[seq];
+  const float d_skip = skip != nullptr ? skip[head] : 0.0f;
+  pdl_wait();
+  if (first >= last) return;
+  float* mine = state + (((size_t)slot * heads + head) * DIM) * vdim + column;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) s[r] = live ? mine[(size_t)(part * ROWS + r) * vdim] : 0.0f;
+
+  auto stage = [&](int buffer, int base) {
+    const int count = min(GS_TOKENS, last - base);
+    // q and k: 2 * DIM floats per token in units of four; unit u of a token covers rows 4u .. 4u + 3 of q (then of k)
+    for (int e = threadIdx.x; e < count * (2 * DIM / 4); e += blockDim.x) {
+      const int n = e / (2 * DIM / 4), u = e - n * (2 * DIM / 4);
+      const int which = u / (DIM / 4), row = (u - which * (DIM / 4)) * 4;
+      cp_async16(&qk_s[buffer][n][which * 8 * PITCH + (row / ROWS) * PITCH + row % ROWS],
+                 qk + ((size_t)(base + n) * groups + group) * 2 * DIM + which * DIM + row);
+    }
+    for (int e = threadIdx.x; e < count * GR_COLS; e += blockDim.x) {
+      const int n = e / GR_COLS, c = e - n * GR_COLS;
+      if (blockIdx.x * GR_COLS + c < vdim)
+        cp_async4(&v_s[buffer][n][c], v + ((size_t)(base + n) * heads + head) * vdim + blockIdx.x * GR_COLS + c);
+    }
+    for (int e = threadIdx.x; e < count * 2; e += blockDim.x)
+      cp_async4(&g_s[buffer][e >> 1][e & 1], gates + ((size_t)(base + (e >> 1)) * heads + head) * 2 + (e & 1));
+    cp_async_commit();
+  };
+
+  stage(0, first);
+  int buffer = 0;
+  for (int base = first; base < last; base += GS_TOKENS, buffer ^= 1) {
+    if (base + GS_TOKENS < last) {
+      stage(buffer ^ 1, base + GS_TOKENS);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int count = min(GS_TOKENS, last - base);
+    for (int n = 0; n < count; ++n) {
+      const float4* qv = reinterpret_cast<const float4*>(&qk_s[buffer][n][part * PITCH]);
+      const float4* kv = reinterpret_cast<const float4*>(&qk_s[buffer][n][8 * PITCH + part * PITCH]);
+      const float value = live ? v_s[buffer][n][local] : 0.0f;
+      const float a = g_s[buffer][n][0], b = g_s[buffer][n][1];
+      float k[ROWS];
+      float seen = 0.0f;
+#pragma unroll
+      for (int r = 0; r < ROWS; r += 4) {
+        const float4 kk = kv[r / 4];
+        k[r] = kk.x; k[r + 1] = kk.y; k[r + 2] = kk.z; k[r + 3] = kk.w;
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        s[r] *= a;
+        if (DELTA) seen = fmaf(s[r], k[r], seen);
+      }
+      if (DELTA) {
+        seen += __shfl_xor_sync(0xffffffffu, seen, 1);
+        seen += __shfl_xor_sync(0xffffffffu, seen, 2);
+        seen += __shfl_xor_sync(0xffffffffu, seen, 4);
+      }
+      const float u = b * (value - seen);
+      float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+      for (int r = 0; r < ROWS; r += 4) {
+        const float4 qq = qv[r / 4];
+        s[r] = fmaf(k[r], u, s[r]);
+        s[r + 1] = fmaf(k[r + 1], u, s[r + 1]);
+        s[r + 2] = fmaf(k[r + 2], u, s[r + 2]);
+        s[r + 3] = fmaf(k[r + 3], u, s[r + 3]);
+        acc0 = fmaf(s[r], qq.x, acc0);
+        acc1 = fmaf(s[r + 1], qq.y, acc1);
+        acc0 = fmaf(s[r + 2], qq.z, acc0);
+        acc1 = fmaf(s[r + 3], qq.w, acc1);
+      }
+      float acc = acc0 + acc1;
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (live && part == 0) out[((size_t)(base + n) * heads + head) * vdim + column] = fmaf(d_skip, value, acc);
+    }
+    __syncthreads();                                   // the buffer is copied into again two rounds on
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+    if (live) mine[(size_t)(part * ROWS + r) * vdim] = s[r];
+}
+
 template <bool DELTA>
 int launch_gated_rule_scan(const float* qk, const float* v, const float* gates, const float* skip, int heads, int groups,
                            int dim, int vdim, float* state, const int* slots, const int* q_start, float* out, int num_seqs,
-                           cudaStream_t stream) {
+                           bool portions, cudaStream_t stream) {
   const dim3 grid((vdim + GR_COLS - 1) / GR_COLS, heads, num_seqs), block(GR_WARPS * 32);
+  if (portions && (dim == 32 || dim == 64 || dim == 128 || dim == 256) && (uintptr_t)qk % 16 == 0) {
+#define TGE_GS_CASE(R)                                                                                                  \
+  if (dim == 8 * R) {                                                                                                  \
+    tge_launch(gated_rule_scan_staged_kernel<R, DELTA>, grid, block, 0, stream, qk, v, gates, skip, heads, groups, vdim, \
+               state, slots, q_start, out);                                                                            \
+    return tge_launched("gated_rule_scan_staged", 1);                                                                  \
+  }
+    TGE_GS_CASE(4) TGE_GS_CASE(8) TGE_GS_CASE(16) TGE_GS_CASE(32)
+#undef TGE_GS_CASE
+  }
   const int rows = (dim + 7) / 8;
 #define TGE_GR_CASE(R)                                                                                                  \
   if (rows <= R) {                                                                                                     \
@@ -374,8 +508,10 @@ TGE_API int tge_gated_rule_scan(const float* qk, const float* v, const float* ga
   TGE_REQUIRE(num_seqs >= 0 && num_seqs <= 65535 && heads <= 65535, "gated_rule_scan: %d requests in a step", num_seqs);
   if (num_seqs == 0 || tokens == 0) return 0;
   if (delta)
-    return launch_gated_rule_scan<true>(qk, v, gates, skip, heads, groups, dim, vdim, state, slots, q_start, out, num_seqs, stream);
-  return launch_gated_rule_scan<false>(qk, v, gates, skip, heads, groups, dim, vdim, state, slots, q_start, out, num_seqs, stream);
+    return launch_gated_rule_scan<true>(qk, v, gates, skip, heads, groups, dim, vdim, state, slots, q_start, out, num_seqs,
+                                        tokens > num_seqs, stream);
+  return launch_gated_rule_scan<false>(qk, v, gates, skip, heads, groups, dim, vdim, state, slots, q_start, out, num_seqs,
+                                       tokens > num_seqs, stream);
 }
 
 TGE_API int tge_norm_scale_add(float* x, const float* y, long long ldy, const float* weight, int tokens, int width, float alpha,

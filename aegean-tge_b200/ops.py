@@ -180,7 +180,7 @@ def attention_lib(head_dim: int, value_dim: int = 0) -> ctypes.CDLL:
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
                                             _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
-                                            _c_int, _c_int, _c_ptr])
+                                            _c_int, _c_int, _c_ptr, _c_int, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim or lib.tge_attention_mma_value_dim() != value_dim:
@@ -769,7 +769,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     ``values_in_keys`` > 0: a position's value is the first that many numbers of its key entry (a latent cache whose
     entries serve as keys whole and as values in part); ``v_pages`` is then not used and may be None.
     ``dist_bias`` (float32 [heads, span]): a learned bias by distance, added unscaled to the scaled score of the key
-    that lies n positions back, entry min(n, span - 1) of the head's row.  Served by the CUDA-core kernel.
+    that lies n positions back, entry min(n, span - 1) of the head's row; every attention kernel adds it where it
+    scales its scores.
     """
     v_pitch = 0
     if values_in_keys:
@@ -821,7 +822,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
             raise KernelError(f"attention: a bias by distance is [heads, span] (and goes without pooled blocks), got "
                               f"{tuple(dist_bias.shape)}")
         dist_span = dist_bias.shape[1]
-    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok and dist_bias is None
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
                and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim)
                and not (v_pitch and value_dim == head_dim))
     if use_mma:
@@ -856,7 +857,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
                                      split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
-                                     _ptr(sink), int(bool(pool)), v_pitch, _stream()), lib)
+                                     _ptr(sink), int(bool(pool)), v_pitch, _ptr(dist_bias), dist_span, _stream()), lib)
         if pool:
             core_lib = core()
             states = scratch.data_ptr()

@@ -447,8 +447,9 @@ def test_temperature_norm_and_store_of_keys_and_values(ops, dtype, heads, kv_hea
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,far,page", [(8, 40.0, 16), (32, 120.0, 64), (4, 300.0, 16)])
-def test_bias_by_distance_in_the_softmax(ops, dtype, rows, far, page):
+@pytest.mark.parametrize("rows,far,page,dim", [(8, 40.0, 16, 16), (32, 120.0, 64, 64), (4, 300.0, 16, 32), (32, 100.0, 64, 128),
+                                               (16, 33.0, 64, 48)])
+def test_bias_by_distance_in_the_softmax(ops, dtype, rows, far, page, dim):
     """Every row of the table differs from its neighbours by several units, so a distance one off, a wrong row past the
     middle or a scaled bias changes the result; prompts and single tokens, two requests, shuffled pages."""
     from aegean_tge_b200.parts.attention import GQAttention
@@ -456,7 +457,7 @@ def test_bias_by_distance_in_the_softmax(ops, dtype, rows, far, page):
     rng = np.random.default_rng(rows)
     rel = rng.permutation(rows * heads).reshape(rows, heads).astype(np.float64) * 1.5 - rows
     table = GQAttention.expand_distance_bias(torch.from_numpy(rel).float(), far).to(DEV)
-    lengths = [int(far) + 75, 21]
+    lengths = [int(far) + 175, 21]
     k_pages, v_pages, block_table, k_list, _ = paged_cache(lengths, kv_heads, dim, page, TORCH[dtype], DEV, seed=rows)
     for new in ([lengths[0], lengths[1]], [1, 1], [40, 2]):
         starts = [lengths[0] - new[0], lengths[1] - new[1]]
