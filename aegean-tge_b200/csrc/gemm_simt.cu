@@ -18,6 +18,7 @@ enum GemmEpilogue : int {
   GEMM_SWIGLU = 3,     // w rows interleaved (gate_i, up_i): out[m, i] = silu(g) * u, run dtype
   GEMM_GELU = 4,       // out[m, n] = gelu(acc + bias[n]) for n >= act_from (plain below it), run dtype; the erf form
   GEMM_GELU_TANH = 5,  // the same with the tanh approximation 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+  GEMM_GLU_CLAMPED = 6,  // gated like 3 with both halves clamped at L = alpha: min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
 };
 // `alpha` multiplies acc + bias in the three plain epilogues (store, store float32, add): a residual multiplier or a
 // logit scale costs no pass of its own.
@@ -103,13 +104,19 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ x,
   for (int i = 0; i < TM; ++i) {
     const int m = m0 + ty * TM + i;
     if (m >= M) continue;
-    if (epilogue == GEMM_SWIGLU) {
+    if (epilogue == GEMM_SWIGLU || epilogue == GEMM_GLU_CLAMPED) {
 #pragma unroll
       for (int j = 0; j < TN; j += 2) {
         const int n = n0 + tx * TN + j;
         if (n + 1 >= N) continue;
         float g = acc[i][j], u = acc[i][j + 1];
         if (bias) { g += bias[n]; u += bias[n + 1]; }
+        if (epilogue == GEMM_GLU_CLAMPED) {
+          g = fminf(g, alpha);
+          u = fminf(fmaxf(u, -alpha), alpha) + 1.0f;
+          g *= 1.702f;                                   // a = (g / 1.702) sigmoid(g) u below
+          u *= 1.0f / 1.702f;
+        }
         const float a = g / (1.0f + expf(-g)) * u;
         reinterpret_cast<T*>(out)[(size_t)m * ldo + (n >> 1)] = from_float<T>(a);
       }
@@ -146,8 +153,8 @@ TGE_API int tge_gemm_simt(const void* x, long long ldx, const void* w, long long
                           long long ldo, int M, int N, int K, int is_bf16, int epilogue, float alpha, int act_from,
                           cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
-  TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GLU_CLAMPED, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE((epilogue != GEMM_SWIGLU && epilogue != GEMM_GLU_CLAMPED) || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
   TGE_REQUIRE(ldx >= K && ldw >= K, "gemm: row strides %lld/%lld shorter than K=%d", ldx, ldw, K);
   if (M == 0) return 0;
   const size_t elem = is_bf16 ? 2 : 4;

@@ -31,7 +31,9 @@
 #include "common.cuh"
 
 enum GemmEpilogue : int { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_SWIGLU = 3, GEMM_GELU = 4,
-                          GEMM_GELU_TANH = 5 };
+                          GEMM_GELU_TANH = 5, GEMM_GLU_CLAMPED = 6 };
+// GEMM_GLU_CLAMPED: the gated epilogue with both halves clamped at L = `alpha`: g <- min(g, L), u <- clamp(u, -L, L),
+// out = g sigmoid(1.702 g) (u + 1).
 // GEMM_GELU / GEMM_GELU_TANH: bfloat16 out = gelu(acc + bias) in the erf or the tanh form for weight rows n >= act_from,
 // plain acc + bias below (a product over row-concatenated weights may activate only its tail).  `alpha` multiplies
 // acc + bias in the store, store-float32 and add epilogues.
@@ -160,6 +162,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// the clamped gate: g <- min(g, L), u <- clamp(u, -L, L), g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float clamped_gate_mul(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+  return __fdividef(g, 1.0f + __expf(-1.702f * g)) * u;
+}
+__device__ __forceinline__ bool gated_epilogue(int epilogue) { return epilogue == GEMM_SWIGLU || epilogue == GEMM_GLU_CLAMPED; }
 
 // 1 / sqrt(mean square of the row + eps) from the row's sums of squares in slices (added in slice order; the
 // loads of eight slices are in flight together)
@@ -205,7 +214,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + p.alpha * (__uint_as_float(r[j]) + bias);
       continue;
     }
-    if (!p.to_partial && p.epilogue == GEMM_SWIGLU) {
+    if (!p.to_partial && gated_epilogue(p.epilogue)) {
       // Even lanes hold gate rows, odd lanes the matching up rows.  Per pair of token columns one
       // exchange gives the even lane (gate, up) of the first column and the odd lane those of the second.
       const bool odd = lane & 1;
@@ -217,7 +226,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         const int m = m0 + j + (odd ? 1 : 0);
         if (n_ok && m < p.m_tok)
           reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
-              __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
+              __float2bfloat16_rn(p.epilogue == GEMM_SWIGLU ? __fdividef(g, 1.0f + __expf(-g)) * u : clamped_gate_mul(g, u, p.alpha));
       }
       continue;
     }
@@ -662,7 +671,7 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
   pdl_trigger();
   pdl_wait();
   const size_t plane = (size_t)m_tok * n_w;
-  if (epilogue == GEMM_SWIGLU) {
+  if (gated_epilogue(epilogue)) {
     const size_t count = plane / 2;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
       const int m = (int)(i / (n_w / 2)), c = (int)(i % (n_w / 2));
@@ -676,7 +685,8 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
       g *= factor;
       u *= factor;
       if (bias) { g += bias[2 * c]; u += bias[2 * c + 1]; }
-      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu_mul(g, u));
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + c] =
+          __float2bfloat16_rn(epilogue == GEMM_SWIGLU ? silu_mul(g, u) : clamped_gate_mul(g, u, alpha));
     }
     return;
   }
@@ -1409,8 +1419,8 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
                              const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps, float alpha,
                              int act_from, cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
-  TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GLU_CLAMPED, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE((epilogue != GEMM_SWIGLU && epilogue != GEMM_GLU_CLAMPED) || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
   TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
   TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
   if (M == 0) return 0;
@@ -1421,7 +1431,7 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
                           force_splits, false, status, stream, &splits, sums, alpha, act_from);
   if (rc != 1) return rc;
   if (splits > 0) {
-    const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
+    const long long count = (epilogue == GEMM_SWIGLU || epilogue == GEMM_GLU_CLAMPED) ? (long long)M * N / 2 : (long long)M * N;
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     tge_launch(splitk_epilogue_kernel, (int)blocks, 256, 0, stream, (const float*)scratch, bias, out, ldo, M, N, splits,

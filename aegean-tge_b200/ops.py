@@ -17,7 +17,7 @@ import torch
 
 from .csrc import build as _build
 
-GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU, GEMM_GELU, GEMM_GELU_TANH = 0, 1, 2, 3, 4, 5
+GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU, GEMM_GELU, GEMM_GELU_TANH, GEMM_GLU_CLAMPED = 0, 1, 2, 3, 4, 5, 6
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a page id outside the pool",
                4: "a row index outside the batch", 8: "a bounded device-side wait gave up"}
 
@@ -577,6 +577,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
     GEMM_STORE: out [M, N] run dtype.  GEMM_STORE_F32: out [M, N] float32.
     GEMM_ADD_F32: ``out`` (float32 [M, N], required) += product.
     GEMM_SWIGLU: w rows interleaved (gate_i, up_i); out [M, N/2] run dtype.
+    GEMM_GLU_CLAMPED: the same rows, both halves clamped at L = ``alpha``: out = min(g, L) sigmoid(1.702 min(g, L))
+    (clamp(u, -L, L) + 1).
     GEMM_GELU / GEMM_GELU_TANH: out [M, N] run dtype = gelu(product + bias) in the erf / the tanh form for the
     columns from ``act_from`` on, the plain product below (for row-concatenated weights).
     ``alpha`` multiplies product + bias in the store and add epilogues (a residual multiplier, a logit scale).
@@ -603,7 +605,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
         want_shape, want_dtype = (M, N), torch.float32
     elif epilogue == GEMM_STORE_F32:
         want_shape, want_dtype = (M, N), torch.float32
-    elif epilogue == GEMM_SWIGLU:
+    elif epilogue in (GEMM_SWIGLU, GEMM_GLU_CLAMPED):
         want_shape, want_dtype = (M, N // 2), x.dtype
     elif epilogue in (GEMM_STORE, GEMM_GELU, GEMM_GELU_TANH):
         want_shape, want_dtype = (M, N), x.dtype

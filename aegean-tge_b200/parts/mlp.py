@@ -158,7 +158,8 @@ class ClampedGLU(FeedForward):
 
     params: ``hidden_size``, ``intermediate_size``, ``limit`` (L), optional ``alpha`` (default 1.702) and ``up_offset``
     (default 1).  weights: ``gate|up|down.weight``.  Gate and up rows are interleaved at load so that one product
-    yields both, stored in float32; one kernel clamps, gates and writes the rows the down product reads.
+    yields both; with alpha 1.702 and offset 1 its epilogue clamps and gates, otherwise the product is stored in
+    float32 and one kernel clamps, gates and writes the rows the down product reads.
     """
     graph_safe = True
     can_defer_norm = True
@@ -189,7 +190,11 @@ class ClampedGLU(FeedForward):
         return 2.0 * tokens * 3 * self.inner_size * self.hidden
 
     def inner(self, h, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        rows = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_STORE_F32)
+        if self.alpha == 1.702 and self.offset == 1.0:
+            # the product's own epilogue clamps and gates (its constants are these two)
+            return self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_GLU_CLAMPED, out=out, alpha=self.limit)
+        complete = getattr(h, "complete", None)
+        rows = self.ops.linear(h if complete is None else complete(), self.w_gate_up, None, self.ops.GEMM_STORE_F32)
         return self.ops.gated_clamp_act(rows, self.limit, self.alpha, self.offset, self.env.dtype, out=out)
 
     def output_projection(self):

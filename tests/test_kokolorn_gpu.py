@@ -414,6 +414,36 @@ def test_clamped_gate(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,width,inner", [(5, 64, 48), (150, 96, 200), (300, 128, 1024), (3, 100, 35)])
+def test_clamped_gate_as_the_products_epilogue(ops, dtype, tokens, width, inner):
+    """The feed-forward part with the design's constants clamps and gates in the epilogue of its first product (the
+    tensor-core product, its sums over cuts along k, and the CUDA-core product), with other constants in a kernel of
+    its own: both are the plain formula."""
+    from aegean_tge_b200.config import PartSpec
+    from aegean_tge_b200.parts import FEED_FORWARDS, build_part
+    from aegean_tge_b200.parts.base import BuildEnv
+    rng = np.random.default_rng(tokens)
+    W = {"f.gate": rng.standard_normal((inner, width)) * 0.3, "f.up": rng.standard_normal((inner, width)) * 0.3,
+         "f.down": rng.standard_normal((width, inner)) * inner ** -0.5}
+    h = rng.standard_normal((tokens, width))
+    if dtype == "bfloat16":
+        W = {k: _to_bfloat16(v.astype(np.float32)).astype(np.float64) for k, v in W.items()}
+        h = _to_bfloat16(h.astype(np.float32)).astype(np.float64)
+    env = BuildEnv(dtype=TORCH[dtype], device=DEV, hidden_size=width, max_positions=64, page_size=16, ops=ops)
+    for alpha, limit in ((1.702, 0.9), (1.702, 50.0), (1.3, 0.9)):
+        part = build_part(FEED_FORWARDS, PartSpec("clamped_glu", {"hidden_size": width, "intermediate_size": inner, "limit": limit,
+                                                                  "alpha": alpha}), env)
+        part.load({f"{t}.weight": torch.from_numpy(W[f"f.{t}"]).to(DEV, TORCH[dtype]) for t in ("gate", "up", "down")})
+        got = part.forward(torch.from_numpy(h).to(DEV, TORCH[dtype]), None)
+        g = np.minimum(h @ W["f.gate"].T, limit)
+        u = np.clip(h @ W["f.up"].T, -limit, limit)
+        ref = (g * plain.sigmoid(alpha * g) * (u + 1.0)) @ W["f.down"].T
+        if alpha == 1.702:
+            assert rel_error(torch.from_numpy(ref), torch.from_numpy(plain.dense_ff(h, W, "f.", limit))) < 1e-12
+        assert rel_error(got, torch.from_numpy(ref)) < 1.5 * KERNEL_TOL[dtype], (alpha, limit)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,normed,every", [(4, 2, 16, True, 4), (3, 3, 20, False, 7), (8, 1, 64, True, 64), (2, 2, 12, True, 0)])
 def test_temperature_norm_and_store_of_keys_and_values(ops, dtype, heads, kv_heads, dim, normed, every):
     """q normalised and heated by position, the keys normalised into their pages, the values the keys as they arrived."""
