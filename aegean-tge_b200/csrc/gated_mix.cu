@@ -219,10 +219,14 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_kernel(
   }
 }
 
-// The same recurrence for portions of several tokens and keys of 32, 64, 128 or 256 numbers: q, k, v and the gates of
-// 16 tokens (8 with keys of 256) are copied into shared memory ahead of the arithmetic (cp.async, two buffers), so that a token's
-// step waits for shared memory and three butterfly steps, not for the L2.  A lane holds the ROWS consecutive rows
-// part * ROWS .. of its column, read as 16-byte units; the parts' runs are four floats apart in banks.
+// The same recurrence for portions of several tokens and keys of 32, 64, 128 or 256 numbers.  q, k, v and the gates of
+// 16 tokens (8 with keys of 256) are copied into shared memory ahead of the arithmetic (cp.async, two buffers), so a
+// token's step waits for shared memory and one butterfly, not for the L2.  A lane holds the ROWS consecutive rows
+// part * ROWS .. of TWO neighbouring columns (its q and k serve both), read as 16-byte units; the parts' runs are four
+// floats apart in banks.  Both sums over the rows are taken of the decayed OLD state, S^T k and S^T q, together with
+// k . q, in one butterfly: the token's output is (a S)^T q + u (k . q), and only u stands between this token's state
+// and the next one's.  A block of four warps owns 32 columns of one head.
+constexpr int GS_COLS = GR_WARPS * 8;       // columns of a block
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -244,25 +248,28 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
   constexpr int PITCH = ROWS + 4;                      // floats between two parts' runs
   constexpr int VEC = 2 * 8 * PITCH;                   // q then k of one token
   __shared__ __align__(16) float qk_s[2][GS_TOKENS][VEC];
-  __shared__ float v_s[2][GS_TOKENS][GR_COLS];
+  __shared__ float v_s[2][GS_TOKENS][GS_COLS];
   __shared__ __align__(8) float g_s[2][GS_TOKENS][2];
   pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane & 7;
   const int head = blockIdx.y, seq = blockIdx.z;
   const int group = head / (heads / groups);
-  const int local = warp * 4 + (lane >> 3);
-  const int column = blockIdx.x * GR_COLS + local;
-  const bool live = column < vdim;
+  const int local = warp * 8 + (lane >> 3) * 2;        // the first of the lane's two columns, inside the block
+  const int column = blockIdx.x * GS_COLS + local;
+  const bool live0 = column < vdim, live1 = column + 1 < vdim;
   const int first = q_start[seq], last = q_start[seq + 1];
   const int slot = slots[seq];
   const float d_skip = skip != nullptr ? skip[head] : 0.0f;
   pdl_wait();
   if (first >= last) return;
   float* mine = state + (((size_t)slot * heads + head) * DIM) * vdim + column;
-  float s[ROWS];
+  float s0[ROWS], s1[ROWS];
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) s[r] = live ? mine[(size_t)(part * ROWS + r) * vdim] : 0.0f;
+  for (int r = 0; r < ROWS; ++r) {
+    s0[r] = live0 ? mine[(size_t)(part * ROWS + r) * vdim] : 0.0f;
+    s1[r] = live1 ? mine[(size_t)(part * ROWS + r) * vdim + 1] : 0.0f;
+  }
 
   auto stage = [&](int buffer, int base) {
     const int count = min(GS_TOKENS, last - base);
@@ -273,10 +280,10 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
       cp_async16(&qk_s[buffer][n][which * 8 * PITCH + (row / ROWS) * PITCH + row % ROWS],
                  qk + ((size_t)(base + n) * groups + group) * 2 * DIM + which * DIM + row);
     }
-    for (int e = threadIdx.x; e < count * GR_COLS; e += blockDim.x) {
-      const int n = e / GR_COLS, c = e - n * GR_COLS;
-      if (blockIdx.x * GR_COLS + c < vdim)
-        cp_async4(&v_s[buffer][n][c], v + ((size_t)(base + n) * heads + head) * vdim + blockIdx.x * GR_COLS + c);
+    for (int e = threadIdx.x; e < count * GS_COLS; e += blockDim.x) {
+      const int n = e / GS_COLS, c = e - n * GS_COLS;
+      if (blockIdx.x * GS_COLS + c < vdim)
+        cp_async4(&v_s[buffer][n][c], v + ((size_t)(base + n) * heads + head) * vdim + blockIdx.x * GS_COLS + c);
     }
     for (int e = threadIdx.x; e < count * 2; e += blockDim.x)
       cp_async4(&g_s[buffer][e >> 1][e & 1], gates + ((size_t)(base + (e >> 1)) * heads + head) * 2 + (e & 1));
@@ -294,53 +301,70 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
     }
     __syncthreads();
     const int count = min(GS_TOKENS, last - base);
-    for (int n = 0; n < count; ++n) {
+    float q[ROWS], k[ROWS];
+    auto fetch = [&](int n) {
       const float4* qv = reinterpret_cast<const float4*>(&qk_s[buffer][n][part * PITCH]);
       const float4* kv = reinterpret_cast<const float4*>(&qk_s[buffer][n][8 * PITCH + part * PITCH]);
-      const float value = live ? v_s[buffer][n][local] : 0.0f;
-      const float a = g_s[buffer][n][0], b = g_s[buffer][n][1];
-      float k[ROWS];
-      float seen = 0.0f;
 #pragma unroll
       for (int r = 0; r < ROWS; r += 4) {
-        const float4 kk = kv[r / 4];
+        const float4 qq = qv[r / 4], kk = kv[r / 4];
+        q[r] = qq.x; q[r + 1] = qq.y; q[r + 2] = qq.z; q[r + 3] = qq.w;
         k[r] = kk.x; k[r + 1] = kk.y; k[r + 2] = kk.z; k[r + 3] = kk.w;
       }
+    };
+    fetch(0);
+    for (int n = 0; n < count; ++n) {
+      const float value0 = live0 ? v_s[buffer][n][local] : 0.0f;
+      const float value1 = live1 ? v_s[buffer][n][local + 1] : 0.0f;
+      const float a = g_s[buffer][n][0], b = g_s[buffer][n][1];
+      float seen0[2] = {0.0f, 0.0f}, seen1[2] = {0.0f, 0.0f}, read0[2] = {0.0f, 0.0f}, read1[2] = {0.0f, 0.0f};
+      float kq[2] = {0.0f, 0.0f};
+      float kr[ROWS];
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
-        s[r] *= a;
-        if (DELTA) seen = fmaf(s[r], k[r], seen);
+        s0[r] *= a;
+        s1[r] *= a;
+        kr[r] = k[r];
+        if (DELTA) {
+          seen0[r & 1] = fmaf(s0[r], k[r], seen0[r & 1]);
+          seen1[r & 1] = fmaf(s1[r], k[r], seen1[r & 1]);
+        }
+        read0[r & 1] = fmaf(s0[r], q[r], read0[r & 1]);
+        read1[r & 1] = fmaf(s1[r], q[r], read1[r & 1]);
+        kq[r & 1] = fmaf(k[r], q[r], kq[r & 1]);
       }
-      if (DELTA) {
-        seen += __shfl_xor_sync(0xffffffffu, seen, 1);
-        seen += __shfl_xor_sync(0xffffffffu, seen, 2);
-        seen += __shfl_xor_sync(0xffffffffu, seen, 4);
-      }
-      const float u = b * (value - seen);
-      float acc0 = 0.0f, acc1 = 0.0f;
+      if (n + 1 < count) fetch(n + 1);                 // the next token's q and k, while the sums cross the lanes
+      float p0 = seen0[0] + seen0[1], p1 = seen1[0] + seen1[1];
+      float o0 = read0[0] + read0[1], o1 = read1[0] + read1[1], dot = kq[0] + kq[1];
 #pragma unroll
-      for (int r = 0; r < ROWS; r += 4) {
-        const float4 qq = qv[r / 4];
-        s[r] = fmaf(k[r], u, s[r]);
-        s[r + 1] = fmaf(k[r + 1], u, s[r + 1]);
-        s[r + 2] = fmaf(k[r + 2], u, s[r + 2]);
-        s[r + 3] = fmaf(k[r + 3], u, s[r + 3]);
-        acc0 = fmaf(s[r], qq.x, acc0);
-        acc1 = fmaf(s[r + 1], qq.y, acc1);
-        acc0 = fmaf(s[r + 2], qq.z, acc0);
-        acc1 = fmaf(s[r + 3], qq.w, acc1);
+      for (int step = 1; step < 8; step <<= 1) {
+        if (DELTA) {
+          p0 += __shfl_xor_sync(0xffffffffu, p0, step);
+          p1 += __shfl_xor_sync(0xffffffffu, p1, step);
+        }
+        o0 += __shfl_xor_sync(0xffffffffu, o0, step);
+        o1 += __shfl_xor_sync(0xffffffffu, o1, step);
+        dot += __shfl_xor_sync(0xffffffffu, dot, step);
       }
-      float acc = acc0 + acc1;
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (live && part == 0) out[((size_t)(base + n) * heads + head) * vdim + column] = fmaf(d_skip, value, acc);
+      const float u0 = b * (value0 - p0), u1 = b * (value1 - p1);
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        s0[r] = fmaf(kr[r], u0, s0[r]);
+        s1[r] = fmaf(kr[r], u1, s1[r]);
+      }
+      if (part == 0) {
+        float* dst = out + ((size_t)(base + n) * heads + head) * vdim + column;
+        if (live0) dst[0] = fmaf(d_skip, value0, fmaf(u0, dot, o0));
+        if (live1) dst[1] = fmaf(d_skip, value1, fmaf(u1, dot, o1));
+      }
     }
     __syncthreads();                                   // the buffer is copied into again two rounds on
   }
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r)
-    if (live) mine[(size_t)(part * ROWS + r) * vdim] = s[r];
+  for (int r = 0; r < ROWS; ++r) {
+    if (live0) mine[(size_t)(part * ROWS + r) * vdim] = s0[r];
+    if (live1) mine[(size_t)(part * ROWS + r) * vdim + 1] = s1[r];
+  }
 }
 
 template <bool DELTA>
@@ -349,6 +373,7 @@ int launch_gated_rule_scan(const float* qk, const float* v, const float* gates, 
                            bool portions, cudaStream_t stream) {
   const dim3 grid((vdim + GR_COLS - 1) / GR_COLS, heads, num_seqs), block(GR_WARPS * 32);
   if (portions && (dim == 32 || dim == 64 || dim == 128 || dim == 256) && (uintptr_t)qk % 16 == 0) {
+    const dim3 grid((vdim + GS_COLS - 1) / GS_COLS, heads, num_seqs);
 #define TGE_GS_CASE(R)                                                                                                  \
   if (dim == 8 * R) {                                                                                                  \
     tge_launch(gated_rule_scan_staged_kernel<R, DELTA>, grid, block, 0, stream, qk, v, gates, skip, heads, groups, vdim, \
