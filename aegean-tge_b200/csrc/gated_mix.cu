@@ -225,8 +225,8 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_kernel(
 // part * ROWS .. of TWO neighbouring columns (its q and k serve both), read as 16-byte units; the parts' runs are four
 // floats apart in banks.  Both sums over the rows are taken of the decayed OLD state, S^T k and S^T q, together with
 // k . q, in one butterfly: the token's output is (a S)^T q + u (k . q), and only u stands between this token's state
-// and the next one's.  A block of four warps owns 32 columns of one head.
-constexpr int GS_COLS = GR_WARPS * 8;       // columns of a block
+// and the next one's.  PARTS lanes (8 or 16) share a column pair: with 16 a block of four warps owns 16 columns, a
+// head is spread over twice as many warps, and each warp has half the arithmetic between two butterflies.
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -238,24 +238,25 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <int ROWS, bool DELTA>
+template <int ROWS, int PARTS, bool DELTA>
 __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
     const float* __restrict__ qk, const float* __restrict__ v, const float* __restrict__ gates,
     const float* __restrict__ skip, int heads, int groups, int vdim, float* __restrict__ state,
     const int* __restrict__ slots, const int* __restrict__ q_start, float* __restrict__ out) {
-  constexpr int DIM = ROWS * 8;
-  constexpr int GS_TOKENS = ROWS > 16 ? 8 : 16;       // tokens per buffer: both buffers within 48 KB
+  constexpr int DIM = ROWS * PARTS;
+  constexpr int GS_COLS = GR_WARPS * 2 * (32 / PARTS); // columns of a block
   constexpr int PITCH = ROWS + 4;                      // floats between two parts' runs
-  constexpr int VEC = 2 * 8 * PITCH;                   // q then k of one token
+  constexpr int VEC = 2 * PARTS * PITCH;               // q then k of one token
+  constexpr int GS_TOKENS = VEC > 320 ? 8 : 16;        // tokens per buffer: both buffers within 48 KB
   __shared__ __align__(16) float qk_s[2][GS_TOKENS][VEC];
   __shared__ float v_s[2][GS_TOKENS][GS_COLS];
   __shared__ __align__(8) float g_s[2][GS_TOKENS][2];
   pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int part = lane & 7;
+  const int part = lane & (PARTS - 1);
   const int head = blockIdx.y, seq = blockIdx.z;
   const int group = head / (heads / groups);
-  const int local = warp * 8 + (lane >> 3) * 2;        // the first of the lane's two columns, inside the block
+  const int local = (warp * (32 / PARTS) + lane / PARTS) * 2;      // the first of the lane's two columns, inside the block
   const int column = blockIdx.x * GS_COLS + local;
   const bool live0 = column < vdim, live1 = column + 1 < vdim;
   const int first = q_start[seq], last = q_start[seq + 1];
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
     for (int e = threadIdx.x; e < count * (2 * DIM / 4); e += blockDim.x) {
       const int n = e / (2 * DIM / 4), u = e - n * (2 * DIM / 4);
       const int which = u / (DIM / 4), row = (u - which * (DIM / 4)) * 4;
-      cp_async16(&qk_s[buffer][n][which * 8 * PITCH + (row / ROWS) * PITCH + row % ROWS],
+      cp_async16(&qk_s[buffer][n][which * PARTS * PITCH + (row / ROWS) * PITCH + row % ROWS],
                  qk + ((size_t)(base + n) * groups + group) * 2 * DIM + which * DIM + row);
     }
     for (int e = threadIdx.x; e < count * GS_COLS; e += blockDim.x) {
@@ -304,7 +305,7 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
     float q[ROWS], k[ROWS];
     auto fetch = [&](int n) {
       const float4* qv = reinterpret_cast<const float4*>(&qk_s[buffer][n][part * PITCH]);
-      const float4* kv = reinterpret_cast<const float4*>(&qk_s[buffer][n][8 * PITCH + part * PITCH]);
+      const float4* kv = reinterpret_cast<const float4*>(&qk_s[buffer][n][PARTS * PITCH + part * PITCH]);
 #pragma unroll
       for (int r = 0; r < ROWS; r += 4) {
         const float4 qq = qv[r / 4], kk = kv[r / 4];
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
       float p0 = seen0[0] + seen0[1], p1 = seen1[0] + seen1[1];
       float o0 = read0[0] + read0[1], o1 = read1[0] + read1[1], dot = kq[0] + kq[1];
 #pragma unroll
-      for (int step = 1; step < 8; step <<= 1) {
+      for (int step = 1; step < PARTS; step <<= 1) {
         if (DELTA) {
           p0 += __shfl_xor_sync(0xffffffffu, p0, step);
           p1 += __shfl_xor_sync(0xffffffffu, p1, step);
@@ -373,14 +374,18 @@ int launch_gated_rule_scan(const float* qk, const float* v, const float* gates, 
                            bool portions, cudaStream_t stream) {
   const dim3 grid((vdim + GR_COLS - 1) / GR_COLS, heads, num_seqs), block(GR_WARPS * 32);
   if (portions && (dim == 32 || dim == 64 || dim == 128 || dim == 256) && (uintptr_t)qk % 16 == 0) {
-    const dim3 grid((vdim + GS_COLS - 1) / GS_COLS, heads, num_seqs);
-#define TGE_GS_CASE(R)                                                                                                  \
-  if (dim == 8 * R) {                                                                                                  \
-    tge_launch(gated_rule_scan_staged_kernel<R, DELTA>, grid, block, 0, stream, qk, v, gates, skip, heads, groups, vdim, \
-               state, slots, q_start, out);                                                                            \
-    return tge_launched("gated_rule_scan_staged", 1);                                                                  \
+    // eight lanes to a column pair at keys of 32 and 128, sixteen at 64 and 256 (measured at 2,048 tokens, 28 heads:
+    // keys of 128: 960 us with eight, 1,036 with sixteen; keys of 64: 657 with eight, 494 with sixteen)
+    const int parts = (dim == 64 || dim == 256) ? 16 : 8;
+    const int cols = GR_WARPS * 2 * (32 / parts);
+    const dim3 grid((vdim + cols - 1) / cols, heads, num_seqs);
+#define TGE_GS_CASE(R, P)                                                                                                  \
+  if (dim == R * P && parts == P) {                                                                                       \
+    tge_launch(gated_rule_scan_staged_kernel<R, P, DELTA>, grid, block, 0, stream, qk, v, gates, skip, heads, groups, vdim, \
+               state, slots, q_start, out);                                                                               \
+    return tge_launched("gated_rule_scan_staged", 1);                                                                     \
   }
-    TGE_GS_CASE(4) TGE_GS_CASE(8) TGE_GS_CASE(16) TGE_GS_CASE(32)
+    TGE_GS_CASE(4, 8) TGE_GS_CASE(16, 8) TGE_GS_CASE(4, 16) TGE_GS_CASE(16, 16)
 #undef TGE_GS_CASE
   }
   const int rows = (dim + 7) / 8;
