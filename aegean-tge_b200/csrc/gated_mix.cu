@@ -302,8 +302,12 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
     }
     __syncthreads();
     const int count = min(GS_TOKENS, last - base);
-    float q[ROWS], k[ROWS];
+    float q[ROWS], k[ROWS], next_value0, next_value1, next_a, next_b;
     auto fetch = [&](int n) {
+      next_value0 = live0 ? v_s[buffer][n][local] : 0.0f;
+      next_value1 = live1 ? v_s[buffer][n][local + 1] : 0.0f;
+      next_a = g_s[buffer][n][0];
+      next_b = g_s[buffer][n][1];
       const float4* qv = reinterpret_cast<const float4*>(&qk_s[buffer][n][part * PITCH]);
       const float4* kv = reinterpret_cast<const float4*>(&qk_s[buffer][n][PARTS * PITCH + part * PITCH]);
 #pragma unroll
@@ -314,10 +318,9 @@ __global__ void __launch_bounds__(GR_WARPS * 32) gated_rule_scan_staged_kernel(
       }
     };
     fetch(0);
+#pragma unroll 2
     for (int n = 0; n < count; ++n) {
-      const float value0 = live0 ? v_s[buffer][n][local] : 0.0f;
-      const float value1 = live1 ? v_s[buffer][n][local + 1] : 0.0f;
-      const float a = g_s[buffer][n][0], b = g_s[buffer][n][1];
+      const float value0 = next_value0, value1 = next_value1, a = next_a, b = next_b;
       float seen0[2] = {0.0f, 0.0f}, seen1[2] = {0.0f, 0.0f}, read0[2] = {0.0f, 0.0f}, read1[2] = {0.0f, 0.0f};
       float kq[2] = {0.0f, 0.0f};
       float kr[ROWS];
