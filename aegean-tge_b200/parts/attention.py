@@ -215,7 +215,7 @@ class GQAttention(Mixer):
     @staticmethod
     def distance_row(n: int, rows: int, far: float) -> int:
         """The table row of distance n: n itself below rows/2; beyond, rows/2 + floor(ln(n / (rows/2)) / ln(far /
-        (rows/2)) * (rows - rows/2)), and never past the last row."""
+        (rows/2)) * (rows - rows/2)), and never past the last row (rows/2 a whole number, rounded down)."""
         half = rows // 2
         if n < half:
             return n
@@ -226,8 +226,8 @@ class GQAttention(Mixer):
         """``rel`` [rows, heads] -> float32 [heads, span], one entry per distance up to the first that reaches the last
         row (every larger distance shares it): what the attention kernels index by min(distance, span - 1)."""
         rows = rel.shape[0]
-        if rows < 2 or rows % 2 or not far > rows // 2:
-            raise ValueError(f"attention: a bias by distance needs an even number of rows (got {rows}) and far > rows/2 (got {far})")
+        if rows < 2 or not far > rows // 2:
+            raise ValueError(f"attention: a bias by distance needs two rows or more (got {rows}) and far > rows/2 (got {far})")
         picks = []
         n = 0
         while True:

@@ -96,7 +96,7 @@ def test_what_a_model_may_leave_out():
     assert spec.schedule == (0, 1, 2, 3) and spec.layers[0].entry.params == {"hidden_size": 24, "index": 0, "count": 1}
 
 
-@pytest.mark.parametrize("rows,far", [(32, 120.0), (8, 100.0), (16, 16.5), (2, 40.0), (64, 4096.0), (32, 128.0)])
+@pytest.mark.parametrize("rows,far", [(32, 120.0), (8, 100.0), (16, 16.5), (2, 40.0), (64, 4096.0), (32, 128.0), (7, 30.0)])
 def test_rows_of_the_bias_by_distance(rows, far):
     import torch
     for n in range(0, int(far) + 40):
@@ -110,7 +110,9 @@ def test_rows_of_the_bias_by_distance(rows, far):
         if 0 <= n < span:
             assert table[:, n].tolist() == rel[plain.distance_bucket(n, rows, far)].tolist()
     with pytest.raises(ValueError):
-        GQAttention.expand_distance_bias(rel[:rows - 1] if rows > 2 else rel[:1], far)
+        GQAttention.expand_distance_bias(rel[:1], far)
+    with pytest.raises(ValueError):
+        GQAttention.expand_distance_bias(rel, float(rows // 2))
 
 
 def test_a_parameter_may_leave_an_extent_to_the_tensor():
