@@ -32,7 +32,9 @@ from ..weights.draws import Draw, normal, uniform
 NO_POSITION_LIMIT = 2 ** 31 - 1      # the design states no longest sequence
 SWISH_ALPHA = 1.702                  # the dense feed-forward's gate is g sigmoid(1.702 g)
 UNIT_EPS = 1e-6                      # q and k of the delta rule: x / sqrt(sum x^2 + 1e-6)
-REL_ROWS = 32                        # rows of the bias by distance in models drawn at random
+def rel_rows(bias_max: float) -> int:
+    """Rows of the bias by distance in models drawn at random (a checkpoint's table brings its own count)."""
+    return 32 if bias_max >= 64.0 else 16
 
 
 def _norm(config: KokolornConfig, name: str) -> PartSpec:
@@ -173,7 +175,7 @@ def random_plan(config: KokolornConfig) -> Iterator[Tuple[str, Tuple[int, ...], 
                 yield q + "k.norm", (a.dim,), "vector", uniform(0.9, 1.1)
             else:
                 yield q + "o.b", (w,), "vector", normal(0.1)
-                yield q + "rel", (REL_ROWS, a.heads), "vector", normal(0.5)
+                yield q + "rel", (rel_rows(a.bias_max), a.heads), "vector", normal(0.5)
         if isinstance(m, DeltaMixer):
             q = p + "mix."
             for t, rows in (("q", m.kv_heads * m.dim), ("k", m.kv_heads * m.dim), ("v", m.heads * m.vdim)):

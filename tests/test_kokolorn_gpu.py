@@ -3,7 +3,7 @@
 First every mechanism alone through its kernel (the recurrence in both forms with its state in slots, what readies its
 inputs with the convolution's tail, the gate before the norm, the normalised sum of branches, the clamped gate, the
 queries' temperature with the store of keys and values, the bias by distance), with inputs made so that a lost state, a
-key one position off or a wrong row of the bias shows; then whole models of four small configurations that differ in
+key one position off or a wrong row of the bias shows; then whole models of five small configurations that differ in
 every size, order and option, cut and batched in every way, in both number formats.
 """
 import json
@@ -94,11 +94,18 @@ def _configs():
             _layer("delta", _delta(4, 2, 128, 128, 4), _dense(192, 1.0)),
             _layer("parallel", {"left": _att(4, 1, 128, 0.1, temp=(0.5, 128), bias_max=200.0), "right": _ssm(4, 64, 128, 1, 2, 4)},
                    _dense(128, 2.0))]),
+        # many query heads to a kv head, head sizes that only the mma.sync kernels take (96, 80), keys of 64 for the
+        # recurrence, two taps, many experts with several chosen, three passes from the first layer on, a layer after them
+        "E": _config(250, 160, 1e-6, [
+            _layer("attention", _att(16, 2, 96, 0.15, temp=(0.25, 48)), _moe(40, 32, 6, shared=56)),
+            _layer("delta", _delta(8, 2, 64, 32, 2), None),
+            _layer("parallel", {"left": _att(8, 1, 80, 0.2, temp=(0.4, 20), bias_max=40.0), "right": _ssm(8, 24, 64, 4, 4, 2)},
+                   _dense(96, 3.0))], loop=(0, 2, 3), scale=0.9),
     }
 
 
 CONFIGS = _configs()
-SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44}
+SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44, "E": 45}
 
 
 @pytest.fixture(scope="module")
@@ -260,7 +267,8 @@ def _run_scan(ops, qk, v, gates, heads, dim, vdim, lengths, cuts, delta, skip=No
 
 
 @pytest.mark.parametrize("delta", [True, False])
-@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 32, 48), (3, 1, 12, 10), (2, 2, 100, 7), (2, 1, 128, 128), (1, 1, 256, 17)])
+@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 32, 48), (3, 1, 12, 10), (2, 2, 100, 7), (2, 1, 128, 128), (1, 1, 256, 17),
+                                                 (4, 2, 64, 40)])
 def test_recurrence_in_portions_batches_and_slots(ops, delta, heads, groups, dim, vdim):
     rng = np.random.default_rng(heads * 1000 + dim + int(delta))
     lengths = [37, 5, 64]
@@ -478,7 +486,7 @@ def test_temperature_norm_and_store_of_keys_and_values(ops, dtype, heads, kv_hea
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,far,page,dim", [(8, 40.0, 16, 16), (32, 120.0, 64, 64), (4, 300.0, 16, 32), (32, 100.0, 64, 128),
-                                               (16, 33.0, 64, 48)])
+                                               (16, 33.0, 64, 48), (32, 100.0, 64, 256), (9, 60.0, 32, 96)])
 def test_bias_by_distance_in_the_softmax(ops, dtype, rows, far, page, dim):
     """Every row of the table differs from its neighbours by several units, so a distance one off, a wrong row past the
     middle or a scaled bias changes the result; prompts and single tokens, two requests, shuffled pages."""
