@@ -47,7 +47,7 @@ __device__ __forceinline__ float conv_channel(const float* __restrict__ raw, lon
 //   qk[t, g] = (unit(q) dim^-1/2, unit(k)), v[t, h], gates[t, h] = (exp(-exp(A_h) softplus(a + dt_bias_h)), sigmoid(b)).
 // mode 1 (state space): raw = [z | x | B | C | dt], x of heads x vdim, B and C of `groups` x dim; x, B, C convolved.
 //   qk[t, g] = (C, B), v[t, h] = x, gates[t, h] = (exp(-exp(A_h) dt), dt) with dt = softplus(dt + dt_bias_h).
-// One block per token; its warps take the units (q/k groups, value heads, the gates) in turn.
+// One block per token (several for a step of few tokens); its warps take the units (q/k groups, value heads) in turn.
 __global__ void __launch_bounds__(128) gated_prepare_kernel(
     const float* __restrict__ raw, long long ld, int mode, int groups, int heads, int dim, int vdim, int taps,
     const float* __restrict__ conv_w, const float* __restrict__ conv_b, const float* __restrict__ tails,
@@ -69,7 +69,9 @@ __global__ void __launch_bounds__(128) gated_prepare_kernel(
   const int k_at = mode == 0 ? qk_width : v_width;
   const int v_at = mode == 0 ? 2 * qk_width : 0;
   const float* tail = tails != nullptr ? tails + (size_t)slot * (taps - 1) * channels : nullptr;
-  for (int unit = warp; unit < groups + heads; unit += warps) {
+  // the units (q/k groups, value heads) are shared out over the blocks of a token: one block for a long step, several
+  // for a step of few tokens, which would otherwise leave most of the device idle
+  for (int unit = blockIdx.y * warps + warp; unit < groups + heads; unit += gridDim.y * warps) {
     if (unit < groups) {
       float* dst = qk + ((size_t)t * groups + unit) * 2 * dim;
       for (int which = 0; which < 2; ++which) {
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(128) gated_prepare_kernel(
             conv_channel(raw, ld, conv_off, v_at + h * vdim + i, t, first, tail, channels, conv_w, conv_b, taps);
     }
   }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+  for (int h = blockIdx.y == 0 ? threadIdx.x : heads; h < heads; h += blockDim.x) {
     const float* row = raw + (size_t)t * ld;
     float decay, strength;
     if (mode == 0) {
@@ -522,7 +524,8 @@ TGE_API int tge_gated_prepare(const float* raw, long long ld, int mode, int grou
   const long long need = 2LL * groups * dim + (long long)heads * vdim * (mode == 0 ? 2 : 2) + (mode == 0 ? 2 : 1) * heads;
   TGE_REQUIRE(ld >= need, "gated_prepare: rows of %lld numbers, %lld needed", ld, need);
   if (tokens == 0) return 0;
-  tge_launch(gated_prepare_kernel, dim3(tokens), dim3(128), 0, stream, raw, ld, mode, groups, heads, dim, vdim, taps, conv_w,
+  const int slices = tokens >= 256 ? 1 : (groups + heads + 3) / 4;
+  tge_launch(gated_prepare_kernel, dim3(tokens, slices), dim3(128), 0, stream, raw, ld, mode, groups, heads, dim, vdim, taps, conv_w,
              conv_b, (const float*)tails, slots, q_start, seq_of_token, a_log, dt_bias, unit_eps, q_scale, qk, v, gates);
   int rc = tge_launched("gated_prepare", 1);
   if (rc < 0 || taps == 1) return rc;
